@@ -1,0 +1,228 @@
+// Host launchers of the persistent tcgen05 GEMM (gemm_sm100a.cuh): argument validation, TMA
+// descriptor encoding per call (a few hundred nanoseconds of host work, so a changing token count
+// never recompiles anything), grid sizing from the number of co-resident CTA pairs.
+#include <cstdlib>
+#include <cstring>
+#include "../../include/fga.h"
+#include "gemm_sm100a.cuh"
+
+namespace fga {
+
+static int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  const int x = atoi(v);
+  return x > 0 ? x : fallback;
+}
+
+// CTA pairs that can be resident at once. A persistent grid never exceeds it: in recv mode the
+// resident CTAs wait for pusher jobs of every CTA of every rank, so a CTA that is not resident
+// would deadlock the group.
+static int resident_pairs(int threads, int* out) {
+  static thread_local int cached_dev = -1, cached[2] = {0, 0};
+  int dev = 0;
+  FGA_CUDA(cudaGetDevice(&dev));
+  const int slot = threads > 32 * kGemmWarps ? 1 : 0;
+  if (dev != cached_dev) {
+    cached_dev = dev;
+    cached[0] = cached[1] = 0;
+  }
+  if (cached[slot] == 0) {
+    FGA_CUDA(cudaFuncSetAttribute(ulysses_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemBytes));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    FGA_CUDA(cudaOccupancyMaxActiveClusters(&clusters, ulysses_gemm_kernel, &cfg));
+    if (clusters < 1) return set_error(kCudaError, "no CTA pair of the GEMM kernel fits on this device");
+    cached[slot] = clusters;
+  }
+  *out = cached[slot];
+  return kSuccess;
+}
+
+static uint32_t make_idesc(int a_mn, int b_mn, int bn) {
+  // FP32 accumulate, BF16 x BF16, M = 256 across the CTA pair, N = bn.
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+// A/B descriptors. K-major operand [rows, k]: box = 64 K-elements x `box_rows` rows.
+// MN-major operand stored as [k, rows]: box = 64 rows-elements x 64 K rows.
+static int encode_operand(CUtensorMap* map, const void* base, int mn_major, long long rows,
+                          long long k, long long pitch, int box_rows) {
+  if (!mn_major)
+    return encode_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, k, pitch, box_rows, 64);
+  return encode_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, rows, pitch, 64, 64);
+}
+
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& P,
+                  cudaStream_t stream) {
+  const int threads = 32 * (kGemmWarps + (P.mode == kRecv ? kPusherWarps : 0));
+  int pairs = 0;
+  const int rc = resident_pairs(threads, &pairs);
+  if (rc != kSuccess) return rc;
+  const long long tiles = static_cast<long long>(P.m_tiles) * P.n_tiles;
+  if (P.mode != kRecv && tiles < pairs) pairs = static_cast<int>(tiles);
+  ulysses_gemm_kernel<<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, P);
+  FGA_CUDA(cudaGetLastError());
+  return kSuccess;
+}
+
+}  // namespace fga
+
+using namespace fga;
+
+extern "C" {
+
+int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_is_kn,
+                  const void* bias, int segments, int n_segment, const int64_t* const* peer_heads,
+                  int64_t head_rows, int rank, int p, int32_t* status, uint64_t timeout_ns,
+                  void* stream) {
+  FGA_REQUIRE(a && b && peer_heads && status, "fga_gemm_push: null operand, peer table or status");
+  FGA_REQUIRE(segments == 1 || segments == 3 || segments == 4,
+              "Expected one output projection or three/four QKV projections");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_push: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(m >= 1 && k >= 8 && k % 8 == 0, "fga_gemm_push: m >= 1 and k a multiple of 8");
+  FGA_REQUIRE(a_rows >= m && a_rows % 256 == 0 && a_rows <= head_rows,
+              "a_rows must be a tile multiple >= the rows of a and fit the head-side rank block");
+  FGA_REQUIRE(n_segment > 0 && n_segment % (p * 128) == 0,
+              "Push segment width must be a multiple of CP * tile N");
+  for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push: null peer table %d", s);
+  const int n = segments * n_segment;
+  GemmParams P{};
+  P.mode = kPush;
+  P.epi = kEpiBf16;
+  P.bn = (n / 128) % 2 == 0 ? 256 : 128;
+  P.m_tiles = a_rows / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = (k + kTileK - 1) / kTileK;
+  P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
+  P.a_mn = 0;
+  P.b_mn = b_is_kn ? 1 : 0;
+  P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
+  P.rank = rank;
+  P.p = p;
+  P.bias = static_cast<const uint16_t*>(bias);
+  for (int s = 0; s < 4; ++s)
+    P.peer_heads[s] = reinterpret_cast<const long long*>(peer_heads[s < segments ? s : 0]);
+  P.segments = segments;
+  P.heads_per_rank = n_segment / p / 128;
+  P.head_pitch = n_segment / p;
+  P.head_rows = head_rows;
+  P.n_rotate = (P.n_tiles % p == 0) ? rank * (P.n_tiles / p) : 0;
+  P.roles = 1;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb;
+  int rc = encode_operand(&ta, a, 0, m, k, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = b_is_kn ? encode_operand(&tb, b, 1, n, k, n, 0) : encode_operand(&tb, b, 0, n, k, k, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_is_kn, int n,
+                  void* c, const int64_t* peer_recv, const int64_t* peer_counters,
+                  int32_t* counters, const void* const* srcs, int num_in, int src_rows, int split,
+                  int rank, int p, int roles, int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(recv && b && c && peer_recv && peer_counters && counters && srcs && status,
+              "fga_gemm_recv: null argument");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_recv: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(num_in == 1 || num_in == 3 || num_in == 4,
+              "Expected one output projection or three/four QKV projections");
+  FGA_REQUIRE(recv_rows >= 256 && recv_rows % 256 == 0, "fga_gemm_recv: receive rows must be a multiple of 256");
+  FGA_REQUIRE(src_rows >= 1 && src_rows <= recv_rows,
+              "Receive source rows must be positive and fit the receive buffer");
+  FGA_REQUIRE(k % (p * num_in * 128) == 0, "Receive K must split evenly over peers and input segments");
+  FGA_REQUIRE(n >= 128 && n % 128 == 0, "GEMM mode must be push/recv and tile N must divide output width");
+  FGA_REQUIRE(split >= 1 && 128 % split == 0, "FUSED_PUSH_SPLIT must divide 128");
+  FGA_REQUIRE((roles & 3) != 0 && (roles & ~3) == 0, "fga_gemm_recv: roles is a mask of 1 (GEMM) and 2 (pushers)");
+  for (int t = 0; t < num_in; ++t) FGA_REQUIRE(srcs[t], "fga_gemm_recv: null source %d", t);
+  GemmParams P{};
+  P.mode = kRecv;
+  P.epi = kEpiBf16;
+  P.bn = n % 256 == 0 ? 256 : 128;
+  P.m_tiles = recv_rows / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = k / kTileK;
+  P.group_m = env_int("FGA_GROUP_M_RECV", 4);
+  P.a_mn = 0;
+  P.b_mn = b_is_kn ? 1 : 0;
+  P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
+  P.rank = rank;
+  P.p = p;
+  P.c = c;
+  P.c_pitch = n;
+  P.c_rows = recv_rows;
+  P.segments = 1;
+  P.heads_per_rank = k / (p * num_in * 128);
+  P.counters = counters;
+  P.target = p * num_in * split;
+  P.peer_recv = reinterpret_cast<const long long*>(peer_recv);
+  P.peer_counters = reinterpret_cast<const long long*>(peer_counters);
+  for (int t = 0; t < 4; ++t) P.src[t] = srcs[t < num_in ? t : 0];
+  P.num_in = num_in;
+  P.src_rows = src_rows;
+  P.split = split;
+  P.recv_k = k;
+  P.roles = roles;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb;
+  int rc = encode_operand(&ta, recv, 0, recv_rows, k, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = b_is_kn ? encode_operand(&tb, b, 1, n, k, n, 0) : encode_operand(&tb, b, 0, n, k, k, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m, int n, int k,
+                   int64_t lda, int64_t ldb, void* c, int64_t ldc, int out_f32, int accumulate,
+                   int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(a && b && c && status, "fga_gemm_local: null argument");
+  FGA_REQUIRE(m >= 1 && k >= 1 && n >= 128 && n % 128 == 0,
+              "fga_gemm_local: n must be a positive multiple of 128");
+  FGA_REQUIRE(!accumulate || out_f32, "MXFP8 gradient accumulation requires FP32 output");
+  FGA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldc >= n && (ldc * (out_f32 ? 4 : 2)) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(c) % 16 == 0,
+              "fga_gemm_local: operands need 16-byte aligned rows");
+  GemmParams P{};
+  P.mode = kLocal;
+  P.epi = out_f32 ? (accumulate ? kEpiF32Add : kEpiF32Store) : kEpiBf16;
+  P.bn = n % 256 == 0 ? 256 : 128;
+  P.m_tiles = (m + 255) / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = (k + kTileK - 1) / kTileK;
+  P.group_m = env_int("FGA_GROUP_M_LOCAL", 8);
+  P.a_mn = a_is_km ? 1 : 0;
+  P.b_mn = b_is_kn ? 1 : 0;
+  P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
+  P.p = 1;
+  P.c = c;
+  P.c_pitch = ldc;
+  P.c_rows = m;
+  P.segments = 1;
+  P.heads_per_rank = 1;
+  P.roles = 1;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb;
+  int rc = encode_operand(&ta, a, P.a_mn, m, k, lda, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_operand(&tb, b, P.b_mn, n, k, ldb, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,523 @@
+// Persistent 2-CTA tcgen05 GEMM for sm_100a with the Ulysses all-to-all fused in.
+//
+// One kernel, three modes (the reference's UlyssesGemm, fused_gemm_a2a_kernels.py:400-929):
+//   local : C = A * B^T, plain store or FP32 accumulate (weight gradients)
+//   push  : the epilogue stores every finished 128x128 head tile straight into the owning peer's
+//           head-side buffer over NVLink (QKV forward, output-projection dgrad)
+//   recv  : pusher warps copy this rank's head-side input into the peers' receive buffers and
+//           bump per-row-block arrival counters; the TMA producer polls its own counters before
+//           loading a row block (output-projection forward, QKV dgrad)
+//
+// Layout of one CTA pair (cluster 2x1x1): the pair owns a 256 x BN output tile, each CTA 128 rows.
+// Each CTA TMA-loads its own 128 rows of A and its half (BN/2) of B per 64-wide K step; one thread
+// of the leader CTA issues tcgen05.mma.cta_group::2 into TMEM of both CTAs (2 accumulator stages
+// of BN columns each). Four epilogue warps per CTA read TMEM (thread = row), convert, write their
+// own row segment to shared memory and ship it with a 1-D bulk copy (cp.async.bulk) to local or
+// peer global memory; FP32 gradient accumulation uses the bulk reduce-add. No TMA load uses
+// cluster multicast. Every wait is bounded: on expiry the waiter records an error in the caller's
+// status word, all roles drain, TMEM is freed and the kernel returns.
+#pragma once
+#include "ptx.cuh"
+#include "common.cuh"
+
+namespace fga {
+
+constexpr int kStages = 5;
+constexpr int kTileM = 128;             // rows per CTA
+constexpr int kTileK = 64;              // BF16 elements per K step (128 bytes = one swizzle span)
+constexpr int kABytes = kTileM * 128;   // 16 KiB
+constexpr int kBBytes = 128 * 128;      // 16 KiB (BN/2 <= 128 rows)
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSlotPitch = 272;         // per-thread staging row: 256 B payload + 16 B skew
+constexpr int kStagingBytes = 128 * kSlotPitch;
+constexpr int kBarrierBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+constexpr int kGemmWarps = 6;           // TMA, MMA, 4 epilogue
+constexpr int kPusherWarps = 4;
+
+enum GemmMode : int { kLocal = 0, kPush = 1, kRecv = 2 };
+enum EpiMode : int { kEpiBf16 = 0, kEpiF32Store = 1, kEpiF32Add = 2 };
+
+struct GemmParams {
+  // geometry
+  int m_tiles, n_tiles, k_tiles;  // 256-row pair tiles, BN-column tiles, 64-element K steps
+  int bn;                         // 128 or 256
+  int group_m;                    // pair tiles per raster group (N varies fastest inside a group)
+  int a_mn, b_mn;                 // 1 = operand is MN-major in global memory (transposed read)
+  uint32_t idesc;                 // tcgen05 instruction descriptor
+  int mode, epi;
+  int rank, p;
+  // local / recv output
+  void* c;
+  long long c_pitch;  // elements per output row
+  int c_rows;         // rows of c that exist; others are not stored
+  // push
+  const uint16_t* bias;            // BF16 bias indexed by weight row, added in FP32, or null
+  const long long* peer_heads[4];  // device int64[P]: peers' head-side buffer base per segment
+  int segments;                    // 3/4 (QKV/QKVG: weight rows interleaved per head) or 1
+  int heads_per_rank;              // 128-column head tiles owned by each rank
+  long long head_pitch;            // elements per head-side buffer row (H / P)
+  long long head_rows;             // rows of one rank block in the head-side buffers (capacity)
+  int n_rotate;                    // N-tile rotation so that ranks start on different peers
+  // recv
+  int* counters;                   // this rank's arrival counters, one per 128 rows
+  int target;                      // arrivals that complete a row block
+  const long long* peer_recv;      // device int64[P]
+  const long long* peer_counters;  // device int64[P]
+  const void* src[4];              // head-side inputs [P*src_rows, heads_per_rank*128] BF16
+  int num_in, src_rows, split;
+  long long recv_k;                // elements per receive-buffer row
+  int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
+  // bounded waits
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+struct WaitCtx {
+  int* status;
+  unsigned long long timeout_ns;
+  uint32_t abort_flag;  // shared address of this CTA's abort word
+  bool dead;
+};
+
+__device__ __forceinline__ void report(WaitCtx& w, int code, int where, int detail) {
+  if (atomicCAS(w.status, 0, code) == 0) {
+    w.status[1] = where;
+    w.status[2] = detail;
+  }
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(w.abort_flag), "r"(1u) : "memory");
+  w.dead = true;
+}
+
+__device__ __forceinline__ bool should_abort(WaitCtx& w) {
+  uint32_t f;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(f) : "r"(w.abort_flag) : "memory");
+  if (f != 0 || ld_relaxed_sys_s32(w.status) != 0) {
+    w.dead = true;
+    return true;
+  }
+  return false;
+}
+
+// Bounded mbarrier wait. Returns false when the kernel is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtx& w, int where) {
+  if (w.dead) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 0x3ff) == 0) {
+      if (should_abort(w)) return false;
+      if (globaltimer_ns() - t0 > w.timeout_ns) {
+        report(w, kErrPipelineTimeout, where, static_cast<int>(bar));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Bounded acquire-poll of a global counter until it reaches `target`.
+__device__ __forceinline__ bool counter_wait(const int* ctr, int target, WaitCtx& w, int where,
+                                             int detail) {
+  if (w.dead) return false;
+  if (ld_acquire_sys_s32(ctr) >= target) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (ld_acquire_sys_s32(ctr) < target) {
+    nanosleep(256);
+    if ((++it & 0xff) == 0) {
+      if (should_abort(w)) return false;
+      if (globaltimer_ns() - t0 > w.timeout_ns) {
+        report(w, kErrCounterTimeout, where, detail);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+// Tile t of this pair's sequence -> (pair tile along M, tile along N). N varies fastest inside a
+// group of `group_m` pair tiles, so a wave of CTAs stays within a few row blocks (the recv GEMM
+// can start before later blocks arrive; a push wave spreads its stores over all destinations) and
+// each weight tile is reused across the group out of L2.
+__device__ __forceinline__ void tile_coords(const GemmParams& P, int t, int& m, int& n) {
+  const int per_group = P.group_m * P.n_tiles;
+  const int g = t / per_group;
+  const int r = t - g * per_group;
+  const int gm = min(P.group_m, P.m_tiles - g * P.group_m);
+  n = r / gm;
+  m = g * P.group_m + (r - n * gm);
+}
+
+// First B row (weight row / output column) of N tile n. Push mode rotates the N order by rank.
+__device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
+  if (P.mode == kPush) {
+    n += P.n_rotate;
+    if (n >= P.n_tiles) n -= P.n_tiles;
+  }
+  return n * P.bn;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pusher warps (recv mode). Job = (row block, input segment, destination, row sub-block): copy
+// rows [row0, row0 + 128/split) of this rank's head-side input for destination d into d's receive
+// buffer, columns in Megatron order [head][q|k|v|g][D], rows past src_rows as zeros; then one
+// release-increment of d's counter for that row block.
+// Mirrors fused_gemm_a2a_kernels.py:291-380 (_push_one, _push_jobs).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane) {
+  const int hpr = P.heads_per_rank;
+  const int sub_rows = kTileM / P.split;
+  const int jobs_per_block = P.num_in * P.p * P.split;
+  const int row_blocks = P.m_tiles * 2;
+  const long long num_jobs = static_cast<long long>(row_blocks) * jobs_per_block;
+  const int worker = blockIdx.x * kPusherWarps + pusher;
+  const int workers = gridDim.x * kPusherWarps;
+  const int half = lane >> 4;          // two 256-byte units per pass
+  const int off16 = (lane & 15) * 16;  // byte offset inside a unit
+  const long long src_pitch = static_cast<long long>(hpr) * 256;  // bytes per source row
+  const int units = sub_rows * hpr;
+  for (long long job = worker; job < num_jobs; job += workers) {
+    const int mi = static_cast<int>(job / jobs_per_block);
+    int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
+    const int q = rest % P.split;
+    rest /= P.split;
+    const int d = (rest % P.p + P.rank) % P.p;
+    const int t = rest / P.p;
+    const int row0 = mi * kTileM + q * sub_rows;
+    const char* src = static_cast<const char*>(P.src[t]) +
+                      (static_cast<long long>(d) * P.src_rows + row0) * src_pitch;
+    char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
+    for (int base = 0; base < units; base += 16) {
+      uint4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int u = base + 2 * i + half;
+        const int r = u / hpr, j = u - r * hpr;
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (u < units && row0 + r < P.src_rows)
+          v[i] = ld_cs_v4(src + r * src_pitch + j * 256 + off16);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int u = base + 2 * i + half;
+        const int r = u / hpr, j = u - r * hpr;
+        if (u < units) {
+          const long long col = (static_cast<long long>(P.rank * hpr + j) * P.num_in + t) * 128;
+          st_cs_v4(dst + (static_cast<long long>(r) * P.recv_k + col) * 2 + off16, v[i]);
+        }
+      }
+    }
+    // The warp barrier orders every lane's stores before lane 0's release, which is cumulative.
+    __syncwarp();
+    if (lane == 0) red_release_sys_add(reinterpret_cast<int*>(P.peer_counters[d]) + mi, 1);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Epilogue for one 128-row x BN accumulator of this CTA. Thread = output row.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem_acc, int quarter,
+                                              int lane, uint32_t slot, int row, int b_row0,
+                                              uint32_t tempty_leader, bool& stores_pending) {
+  const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+  if (P.epi == kEpiBf16) {
+    const int halves = P.bn >> 7;
+    for (int h = 0; h < halves; ++h) {
+      // Destination of this row's 256-byte segment.
+      char* dst = nullptr;
+      const int unit = (b_row0 >> 7) + h;  // 128-wide head tile index in weight-row order
+      if (P.mode == kPush) {
+        const int head = unit / P.segments, seg = unit - head * P.segments;
+        const int dest = head / P.heads_per_rank, within = head - dest * P.heads_per_rank;
+        dst = reinterpret_cast<char*>(P.peer_heads[seg][dest]) +
+              ((static_cast<long long>(P.rank) * P.head_rows + row) * P.head_pitch + within * 128) * 2;
+      } else if (row < P.c_rows) {
+        dst = static_cast<char*>(P.c) + (static_cast<long long>(row) * P.c_pitch + unit * 128) * 2;
+      }
+      if (stores_pending) bulk_wait_read_all();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + lane_base + h * 128 + c * 32, r);
+        tmem_ld_wait();
+        if (h == halves - 1 && c == 3) {
+          // Last TMEM read of this accumulator stage: hand it back to the MMA thread.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader);
+        }
+        if (P.bias != nullptr) {
+          const uint4* bp = reinterpret_cast<const uint4*>(P.bias + b_row0 + h * 128 + c * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 b = __ldg(bp + v);
+            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              r[v * 8 + e * 2] = __float_as_uint(__uint_as_float(r[v * 8 + e * 2]) +
+                                                 bf16_bits_to_f32(w[e] & 0xffffu));
+              r[v * 8 + e * 2 + 1] = __float_as_uint(__uint_as_float(r[v * 8 + e * 2 + 1]) +
+                                                     bf16_bits_to_f32(w[e] >> 16));
+            }
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint32_t a0 = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+          const uint32_t a1 = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+          const uint32_t a2 = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+          const uint32_t a3 = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + c * 64 + v * 16),
+                       "r"(a0), "r"(a1), "r"(a2), "r"(a3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_shared();
+      if (dst != nullptr) {
+        bulk_store(dst, slot, 256);
+        bulk_commit();
+        stores_pending = true;
+      }
+    }
+  } else {
+    // FP32 output: 64 columns (256 bytes) per piece.
+    const int pieces = P.bn >> 6;
+    for (int s = 0; s < pieces; ++s) {
+      char* dst = nullptr;
+      if (row < P.c_rows)
+        dst = static_cast<char*>(P.c) + (static_cast<long long>(row) * P.c_pitch + b_row0 + s * 64) * 4;
+      if (stores_pending) bulk_wait_read_all();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + lane_base + s * 64 + c * 32, r);
+        tmem_ld_wait();
+        if (s == pieces - 1 && c == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader);
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + c * 128 + v * 16),
+                       "r"(r[v * 4]), "r"(r[v * 4 + 1]), "r"(r[v * 4 + 2]), "r"(r[v * 4 + 3])
+                       : "memory");
+      }
+      fence_proxy_async_shared();
+      if (dst != nullptr) {
+        if (P.epi == kEpiF32Add)
+          bulk_reduce_add_f32(dst, slot, 256);
+        else
+          bulk_store(dst, slot, 256);
+        bulk_commit();
+        stores_pending = true;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel. blockDim = 192 (local, push) or 320 (recv: + 4 pusher warps). Grid = 2 * pairs.
+// ---------------------------------------------------------------------------------------------
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + kPusherWarps), 1)
+    ulysses_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t staging = smem_base + kStages * kStageBytes;
+  const uint32_t bars = staging + kStagingBytes;
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tfull[2], tempty[2]
+  const uint32_t full0 = bars, empty0 = bars + 8 * kStages, tfull0 = bars + 16 * kStages,
+                 tempty0 = tfull0 + 16, tmem_slot = tempty0 + 16, abort_word = tmem_slot + 8;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int pairs = gridDim.x >> 1;
+  const int total_tiles = P.m_tiles * P.n_tiles;
+  const bool gemm_on = (P.roles & 1) != 0;
+
+  WaitCtx w{P.status, P.timeout_ns, abort_word, false};
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full0 + 8 * i, 1);   // leader producer's arrive.expect_tx (+ both CTAs' bytes)
+      mbar_init(empty0 + 8 * i, 1);  // one tcgen05.commit arrival per use
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull0 + 8 * i, 1);   // one tcgen05.commit arrival per tile
+      mbar_init(tempty0 + 8 * i, 8);  // 4 epilogue warps x 2 CTAs
+    }
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_word), "r"(0u) : "memory");
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0 && gemm_on) {
+      const uint32_t tx_bytes = 2u * (kABytes + (P.bn >> 1) * 128u);
+      const int b_half = P.bn >> 1;
+      int s = 0;
+      uint32_t ph = 0;
+      for (int t = pair; t < total_tiles && !w.dead; t += pairs) {
+        int m, n;
+        tile_coords(P, t, m, n);
+        const int a_row0 = m * 256 + static_cast<int>(cta_rank) * kTileM;
+        const int b_row0 = b_row0_of(P, n) + static_cast<int>(cta_rank) * b_half;
+        if (P.mode == kRecv) {
+          // Acquire this CTA's row block from every source, then order the TMA reads after it.
+          const int blk = m * 2 + static_cast<int>(cta_rank);
+          if (!counter_wait(P.counters + blk, P.target, w, 10, blk)) break;
+          fence_proxy_async_global();
+        }
+        for (int kt = 0; kt < P.k_tiles; ++kt) {
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, w, 11)) break;
+          const uint32_t a_dst = smem_base + s * kStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          const uint32_t full_leader = mapa(full0 + 8 * s, 0);
+          if (leader) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
+          const int k0 = kt * kTileK;
+          if (!P.a_mn) {
+            tma_load_2d_pair(a_dst, &tmap_a, full_leader, k0, a_row0);
+          } else {
+            tma_load_2d_pair(a_dst, &tmap_a, full_leader, a_row0, k0);
+            tma_load_2d_pair(a_dst + 8192, &tmap_a, full_leader, a_row0 + 64, k0);
+          }
+          if (!P.b_mn) {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, k0, b_row0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, b_row0, k0);
+            if (b_half > 64) tma_load_2d_pair(b_dst + 8192, &tmap_b, full_leader, b_row0 + 64, k0);
+          }
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA)
+    if (lane == 0 && leader && gemm_on) {
+      // Shared-memory matrix descriptors: SWIZZLE_128B, descriptor version 1.
+      //   K-major : 8-row groups 1024 B apart (SBO); one UMMA_K (16 elements) = 32 bytes.
+      //   MN-major: 64-element chunks 8192 B apart (LBO), 8-K-row groups 1024 B apart (SBO);
+      //             one UMMA_K = 16 K rows = 2048 bytes.
+      const uint64_t desc_hi = (static_cast<uint64_t>(64u | (1u << 14) | (2u << 29))) << 32;
+      const uint32_t a_lbo = P.a_mn ? 512u : 1u, b_lbo = P.b_mn ? 512u : 1u;
+      const uint32_t a_step = P.a_mn ? 128u : 2u, b_step = P.b_mn ? 128u : 2u;
+      int s = 0, as = 0;
+      uint32_t ph = 0, aph = 0;
+      for (int t = pair; t < total_tiles && !w.dead; t += pairs) {
+        if (!mbar_wait(tempty0 + 8 * as, aph ^ 1, w, 20)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * P.bn;
+        for (int kt = 0; kt < P.k_tiles; ++kt) {
+          if (!mbar_wait(full0 + 8 * s, ph, w, 21)) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * kStageBytes;
+          const uint32_t b_addr = a_addr + kABytes;
+          const uint64_t adesc = desc_hi | ((a_addr >> 4) & 0x3fffu) | (a_lbo << 16);
+          const uint64_t bdesc = desc_hi | ((b_addr >> 4) & 0x3fffu) | (b_lbo << 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, P.idesc,
+                          (kt | k) != 0 ? 1u : 0u);
+          tc_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs when the MMAs retire
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (w.dead) break;
+        tc_commit_pair(tfull0 + 8 * as, 3);  // accumulator ready in both CTAs
+        if (++as == 2) {
+          as = 0;
+          aph ^= 1;
+        }
+      }
+    }
+  } else if (warp < kGemmWarps) {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    if (gemm_on) {
+      const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+      const int row_in_cta = quarter * 32 + lane;
+      const uint32_t slot = staging + row_in_cta * kSlotPitch;
+      bool stores_pending = false;
+      int as = 0;
+      uint32_t aph = 0;
+      for (int t = pair; t < total_tiles; t += pairs) {
+        int m, n;
+        tile_coords(P, t, m, n);
+        const bool ok = mbar_wait(tfull0 + 8 * as, aph, w, 30);
+        // All lanes take the same branch: the barrier state is CTA-wide and aborts are sticky.
+        if (!__all_sync(0xffffffffu, ok)) {
+          w.dead = true;
+          break;
+        }
+        tc_fence_after();
+        const int row = m * 256 + static_cast<int>(cta_rank) * kTileM + row_in_cta;
+        epilogue_tile(P, tmem_base + as * P.bn, quarter, lane, slot, row, b_row0_of(P, n),
+                      mapa(tempty0 + 8 * as, 0), stores_pending);
+        if (++as == 2) {
+          as = 0;
+          aph ^= 1;
+        }
+      }
+      // Writes (local or remote) are complete before the kernel ends; the group barrier that
+      // follows a push publishes them with a system-scope release.
+      bulk_wait_all();
+      if (P.mode == kPush) fence_acq_rel_sys();
+    }
+  } else {
+    // ------------------------------------------------------------------ pusher warps (recv mode)
+    if (P.mode == kRecv && (P.roles & 2) != 0) run_pushers(P, warp - kGemmWarps, lane);
+  }
+
+  // Teardown: nobody leaves while the pair may still touch this CTA's shared memory or TMEM.
+  __syncwarp();
+  if (should_abort(w)) {
+    // Loads that were issued but never consumed may still be landing in shared memory.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) nanosleep(1000);
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+}  // namespace fga

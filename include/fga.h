@@ -1,0 +1,130 @@
+/* libfga - C ABI of the B200 (sm_100a) fused projection-GEMM + Ulysses all-to-all path.
+ *
+ * The reference project (niyunsheng/fused-gemm-a2a) has no FFI: its boundary is the Python module
+ * surface of fused_gemm_a2a.py / fused_gemm_a2a_kernels.py, which JIT-compiles CuTe-DSL and Triton
+ * kernels. This header is the boundary a binding of that surface calls instead. Each entry point
+ * names the reference interface it replaces (file:line in the reference tree).
+ *
+ * Conventions
+ *   - plain C: raw device pointers, sizes, a cudaStream_t passed as void*; no torch types.
+ *   - every function returns 0 on success, a negative FgaResult otherwise; fga_last_error()
+ *     returns the message of the calling thread's last failure. Nothing throws.
+ *   - launch functions enqueue on `stream`, never synchronize, never allocate, and are legal
+ *     under CUDA stream capture (except where noted). The current device must be the one the
+ *     pointers live on.
+ *   - `status` is a caller-owned int[4] in device memory, zeroed once by the caller. A kernel
+ *     whose bounded wait expires writes {code, where, detail, 0} (FgaDeviceError) and returns;
+ *     the context stays usable. Kernels never clear it.
+ *   - all matrices are row-major; BF16 is passed as 16-bit words.
+ */
+#ifndef FGA_H_
+#define FGA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum FgaResult {
+  FGA_SUCCESS = 0,
+  FGA_INVALID_ARGUMENT = -1,
+  FGA_CUDA_ERROR = -2,
+  FGA_UNSUPPORTED = -3
+} FgaResult;
+
+typedef enum FgaDeviceError {
+  FGA_DEV_OK = 0,
+  FGA_DEV_BARRIER_TIMEOUT = 1,  /* a peer never published its barrier epoch */
+  FGA_DEV_COUNTER_TIMEOUT = 2,  /* a receive row block never collected all arrivals */
+  FGA_DEV_PIPELINE_TIMEOUT = 3, /* an in-kernel TMA/MMA/epilogue barrier never flipped */
+  FGA_DEV_QUANT_TIMEOUT = 4     /* receive-side quantizer never saw its row block */
+} FgaDeviceError;
+
+#define FGA_IPC_HANDLE_BYTES 64
+
+int fga_version(void);
+const char* fga_last_error(void);
+/* Number of SMs of the current device (grid sizing, also used by the host layer). */
+int fga_sm_count(void);
+
+/* ---- symmetric memory ---------------------------------------------------------------------
+ * Replaces torch symmetric memory with the NVSHMEM backend, used by the reference only to
+ * allocate and rendezvous peer-mapped buffers (fused_gemm_a2a.py:100, 118-127). One allocation
+ * per buffer set; the 64-byte handle is exchanged once over the CP group by the host layer. */
+int fga_symm_alloc(size_t bytes, void** ptr);                        /* cudaMalloc + zero fill */
+int fga_symm_export(void* ptr, unsigned char handle[FGA_IPC_HANDLE_BYTES]);
+int fga_symm_open(const unsigned char handle[FGA_IPC_HANDLE_BYTES], void** peer_ptr);
+int fga_symm_close(void* peer_ptr);
+int fga_symm_free(void* ptr);
+
+/* ---- group barrier ------------------------------------------------------------------------
+ * Replaces barrier / _barrier_kernel (fused_gemm_a2a_kernels.py:204-234; host wrapper
+ * fused_gemm_a2a.py:129-135). flags: this rank's int64[P]; peer_flags: device int64[P] holding
+ * every rank's flags address. bump != 0 zeroes counters[0:count] before publishing and increments
+ * epoch_out[0] afterwards. */
+int fga_barrier(int64_t* flags, const int64_t* peer_flags, int rank, int p, int bump,
+                int32_t* counters, int count, int32_t* epoch_out, int32_t* status,
+                uint64_t timeout_ns, void* stream);
+
+/* ---- fused GEMMs --------------------------------------------------------------------------
+ * Replace _Comm.gemm / UlyssesGemm (fused_gemm_a2a.py:162-234; fused_gemm_a2a_kernels.py:400-929).
+ * b is [n, k] when b_is_kn == 0 and [k, n] otherwise. */
+
+/* push: heads[seg] on peer dest receives rows [rank*head_rows, rank*head_rows + a_rows) of
+ * a[m, k] * b^T (+ bias in FP32 when bias != NULL), one 128-column head tile at a time.
+ * Rows of a beyond m read as zero. peer_heads[s]: device int64[P] of the peers' buffer bases for
+ * segment s (s < segments; segments is 1, 3 or 4). n = segments * n_segment.
+ * Reference: mode 'push' with _tile_mapping and _epilogue_push_simt
+ * (fused_gemm_a2a_kernels.py:617-635, 900-913, 975-1050). */
+int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_is_kn,
+                  const void* bias, int segments, int n_segment, const int64_t* const* peer_heads,
+                  int64_t head_rows, int rank, int p, int32_t* status, uint64_t timeout_ns,
+                  void* stream);
+
+/* recv: pusher warps copy srcs[t][d*src_rows + row, :] (t < num_in) into peer d's receive buffer
+ * in [head][q|k|v|g][128] column order, rows >= src_rows as zeros, and bump peer d's counter of
+ * that 128-row block; the GEMM c[recv_rows, n] = recv[recv_rows, k] * b^T consumes a row block
+ * once its counter reaches p * num_in * split. roles: bit 0 GEMM, bit 1 pushers (both = 3).
+ * Reference: mode 'recv' with _push_jobs / _push_one
+ * (fused_gemm_a2a_kernels.py:291-380, 764-772, 798-804). */
+int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_is_kn, int n,
+                  void* c, const int64_t* peer_recv, const int64_t* peer_counters,
+                  int32_t* counters, const void* const* srcs, int num_in, int src_rows, int split,
+                  int rank, int p, int roles, int32_t* status, uint64_t timeout_ns, void* stream);
+
+/* local: c[m, n] (=|+=) a * b^T with a as [m, k] (a_is_km == 0) or [k, m] (a_is_km != 0, read
+ * transposed) and b as [n, k] or [k, n]. out_f32 selects FP32 output; accumulate (FP32 only) adds
+ * into c. Rows of the reduction axis beyond k read as zero. With a_is_km = b_is_kn = 1 this is
+ * the weight gradient dW = dY^T X with optional accumulation into main_grad.
+ * Reference: _weight_grad (fused_gemm_a2a.py:249-275) and the 'local' mode with
+ * _epilogue_accumulate (fused_gemm_a2a_kernels.py:914-918, 932-972). */
+int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m, int n, int k,
+                   int64_t lda, int64_t ldb, void* c, int64_t ldc, int out_f32, int accumulate,
+                   int32_t* status, uint64_t timeout_ns, void* stream);
+
+/* ---- auxiliary kernels -------------------------------------------------------------------- */
+
+/* Replaces resize_rank_rows (fused_gemm_a2a_kernels.py:1145-1188). in/out: `segments` BF16
+ * matrices [peers*rows_in, width] -> [peers*rows_out, width]. bias may be NULL. */
+int fga_copy_rank_rows(const void* const* in, void* const* out, int segments, int peers,
+                       int64_t rows_in, int64_t rows_out, int width, const void* bias,
+                       int head_dim, int head_offset, void* stream);
+
+/* Replaces reduce_bias_grad (fused_gemm_a2a_kernels.py:1086-1103). scratch: FP32 buffer of
+ * fga_bias_grad_scratch_floats(rows, width) elements in device memory. */
+int64_t fga_bias_grad_scratch_floats(int64_t rows, int width);
+int fga_bias_grad(const void* dy, int64_t rows, int width, void* out, int out_is_f32,
+                  int accumulate, float* scratch, void* stream);
+
+/* Replaces mxfp8_quantize / _mx_quant_kernel (fused_gemm_a2a_kernels.py:1222-1292, 1358-1376).
+ * a: BF16 [rows, k] with element strides (stride_row, stride_k), one of them 1. q: E4M3
+ * [rows_padded, k_padded]; sf: rows_padded*k_padded/32 E8M0 bytes in the tcgen05 128x4 layout. */
+int fga_mx_quantize(const void* a, int64_t rows, int k, int64_t stride_row, int64_t stride_k,
+                    void* q, void* sf, int64_t rows_padded, int k_padded, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FGA_H_ */
