@@ -19,15 +19,13 @@ static int env_int(const char* name, int fallback) {
 // resident CTAs wait for pusher jobs of every CTA of every rank, so a CTA that is not resident
 // would deadlock the group.
 static int resident_pairs(int threads, int* out) {
-  static thread_local int cached_dev = -1, cached[2] = {0, 0};
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices][2];  // 0 = not queried yet; racing threads compute the same value
   int dev = 0;
   FGA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(kUnsupported, "device index %d out of range", dev);
   const int slot = threads > 32 * kGemmWarps ? 1 : 0;
-  if (dev != cached_dev) {
-    cached_dev = dev;
-    cached[0] = cached[1] = 0;
-  }
-  if (cached[slot] == 0) {
+  if (cached[dev][slot] == 0) {
     FGA_CUDA(cudaFuncSetAttribute(ulysses_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemBytes));
     cudaLaunchConfig_t cfg{};
@@ -44,9 +42,9 @@ static int resident_pairs(int threads, int* out) {
     int clusters = 0;
     FGA_CUDA(cudaOccupancyMaxActiveClusters(&clusters, ulysses_gemm_kernel, &cfg));
     if (clusters < 1) return set_error(kCudaError, "no CTA pair of the GEMM kernel fits on this device");
-    cached[slot] = clusters;
+    cached[dev][slot] = clusters;
   }
-  *out = cached[slot];
+  *out = cached[dev][slot];
   return kSuccess;
 }
 

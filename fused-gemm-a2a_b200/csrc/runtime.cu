@@ -25,17 +25,17 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 int sm_count() {
-  static thread_local int cached_dev = -1, cached = 0;
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices];  // 0 = not queried yet
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  if (dev != cached_dev) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  if (cached[dev] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached = n;
-    cached_dev = dev;
+    cached[dev] = n;
   }
-  return cached;
+  return cached[dev];
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 tmap_encoder() {

@@ -1,0 +1,121 @@
+"""The CPU oracle against golden vectors produced by the reference's own unfused Ulysses modules
+(benchmark/reference.py of the reference tree, run under gloo by tests/golden/make_golden.py).
+Float32 inputs, float64 accumulation in the oracle; the reference computed in float32, so outputs
+agree to float32 round-off (1e-4 of each tensor's scale)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.ulysses_oracle import UlyssesOracle, deinterleave_qkv_rows, interleave_qkv_rows
+from tests.golden.make_golden import c1_inputs, sample
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden')
+
+
+def near(actual, expected, what, rel=1e-4):
+    actual, expected = np.asarray(actual, dtype=np.float64), np.asarray(expected, dtype=np.float64)
+    assert actual.shape == expected.shape, what
+    assert np.abs(actual - expected).max() <= rel * max(np.abs(expected).max(), 1e-6), what
+
+
+def tensors(z, p, key):
+    return [torch.from_numpy(z[f'r{r}_{key}']) for r in range(p)]
+
+
+@pytest.mark.parametrize('name,p,hidden,heads,segments,bias', [
+    ('small_p2', 2, 32, 4, 4, True), ('small_p4', 4, 64, 8, 3, False)])
+def test_oracle_reproduces_reference_modules(name, p, hidden, heads, segments, bias):
+    z = np.load(os.path.join(GOLDEN, f'ulysses_{name}.npz'))
+    d = hidden // heads
+    wq = interleave_qkv_rows(torch.from_numpy(z['w']), heads, d)
+    bq = interleave_qkv_rows(torch.from_numpy(z['b']), heads, d) if bias else None
+    wo = torch.from_numpy(z['wo'])
+    bo = torch.from_numpy(z['bo']) if bias else None
+    oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, dtype=torch.float32,
+                           acc_dtype=torch.float64)
+    xs, os_, dys = tensors(z, p, 'x'), tensors(z, p, 'o'), tensors(z, p, 'dy')
+    grads = [tuple(torch.from_numpy(z[f'r{r}_g{i}']) for i in range(segments)) for r in range(p)]
+    outs = oracle.qkv_forward(xs)
+    back = oracle.qkv_backward(xs, grads)
+    ys = oracle.out_forward(os_)
+    dos, out_params = oracle.out_backward(os_, dys)
+    for r in range(p):
+        for i in range(segments):
+            near(outs[r][i], z[f'r{r}_out{i}'], f'rank {r} output {i}')
+        dx, dw, db = back[r]
+        near(dx, z[f'r{r}_dx'], f'rank {r} dx')
+        # the reference holds segment-major parameter gradients, rank-local (not yet all-reduced)
+        near(deinterleave_qkv_rows(dw, heads, d), z[f'r{r}_dw'], f'rank {r} dW_qkv')
+        near(ys[r], z[f'r{r}_y'], f'rank {r} y')
+        near(dos[r], z[f'r{r}_do'], f'rank {r} dO')
+        near(out_params[r][0], z[f'r{r}_dwo'], f'rank {r} dW_o')
+        if bias:
+            near(deinterleave_qkv_rows(db, heads, d), z[f'r{r}_db'], f'rank {r} dbias_qkv')
+            near(out_params[r][1], z[f'r{r}_dbo'], f'rank {r} dbias_o')
+
+
+def test_oracle_reproduces_cpu_benchmark_configuration():
+    """P=2, per-rank M=512, H=1024, 8 heads of 128, fp32, no bias: checksums and strided samples of
+    every output of the reference run."""
+    z = np.load(os.path.join(GOLDEN, 'ulysses_c1_p2.npz'))
+    p, m, hidden, heads = 2, 512, 1024, 8
+    per_rank = [c1_inputs(r, p, m, hidden, heads) for r in range(p)]
+    w, wo = per_rank[0][0], per_rank[0][1]
+    wq = interleave_qkv_rows(torch.cat(w), heads, hidden // heads)
+    oracle = UlyssesOracle(p, hidden, heads, 3, wq, None, wo, None, dtype=torch.float32,
+                           acc_dtype=torch.float64)
+    xs = [t[2] for t in per_rank]
+    grads = [tuple(t[3]) for t in per_rank]
+    os_ = [t[4] for t in per_rank]
+    dys = [t[5] for t in per_rank]
+    outs, back = oracle.qkv_forward(xs), oracle.qkv_backward(xs, grads)
+    ys = oracle.out_forward(os_)
+    dos, out_params = oracle.out_backward(os_, dys)
+    for r in range(p):
+        got = {f'out{i}': outs[r][i] for i in range(3)}
+        got.update(dx=back[r][0], dw=deinterleave_qkv_rows(back[r][1], heads, hidden // heads),
+                   y=ys[r], do=dos[r], dwo=out_params[r][0])
+        for key, value in got.items():
+            value = value.float().numpy()
+            near(sample(value), z[f'r{r}_{key}_sample'], f'rank {r} {key} samples', rel=2e-4)
+            scale = float(z[f'r{r}_{key}_abs'])
+            assert abs(np.abs(value.astype(np.float64)).sum() - scale) <= 1e-5 * scale, key
+            assert abs(value.astype(np.float64).sum() - float(z[f'r{r}_{key}_sum'])) <= 1e-5 * scale, key
+
+
+def test_row_interleave_round_trip():
+    heads, d = 4, 8
+    for s in (3, 4):
+        seg = torch.randn(s * heads * d, 16)
+        inter = interleave_qkv_rows(seg, heads, d)
+        for h in range(heads):
+            for j in range(s):
+                rows = slice((h * s + j) * d, (h * s + j + 1) * d)
+                assert torch.equal(inter[rows], seg[j * heads * d + h * d:j * heads * d + (h + 1) * d])
+        assert torch.equal(deinterleave_qkv_rows(inter, heads, d), seg)
+    with pytest.raises(ValueError):
+        interleave_qkv_rows(torch.randn(5 * heads * d, 16), heads, d)
+
+
+def test_padded_buffers_match_unpadded_flow():
+    """The padded transport model (head-side and receive buffers with pad rows) carries exactly
+    the unpadded results in its logical rows and zeros elsewhere."""
+    torch.manual_seed(0)
+    p, m, hidden, heads, capacity = 4, 37, 64, 8, 48
+    d = hidden // heads
+    wq, wo = torch.randn(3 * hidden, hidden, dtype=torch.float64), torch.randn(hidden, hidden, dtype=torch.float64)
+    oracle = UlyssesOracle(p, hidden, heads, 3, wq, None, wo, None, dtype=torch.float64, acc_dtype=torch.float64)
+    xs = [torch.randn(m, hidden, dtype=torch.float64) for _ in range(p)]
+    outs = oracle.qkv_forward(xs)
+    bufs = oracle.qkv_heads_buffers(xs, capacity)
+    for dest in range(p):
+        for s in range(3):
+            blocks = bufs[dest][s].view(p, capacity, hidden // p)
+            assert torch.equal(blocks[:, :m].reshape(p * m, heads // p, d), outs[dest][s])
+            assert not blocks[:, m:].any()
+    grads = [tuple(torch.randn(p * m, heads // p, d, dtype=torch.float64) for _ in range(3)) for _ in range(p)]
+    for r in range(p):
+        padded = oracle.qkv_recv_buffer(grads, r, capacity)
+        assert torch.equal(padded[:m], oracle.qkv_recv_buffer(grads, r)) and not padded[m:].any()
