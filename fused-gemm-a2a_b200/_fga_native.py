@@ -35,6 +35,7 @@ def _declare(l):
     l.fga_version.restype = i
     l.fga_last_error.restype = c_char_p
     l.fga_sm_count.restype = i
+    l.fga_launch_count.restype = c_uint64
     l.fga_symm_alloc.argtypes = [c_size_t, pp]
     l.fga_symm_export.argtypes = [vp, c_char_p]
     l.fga_symm_open.argtypes = [c_char_p, pp]
@@ -56,7 +57,7 @@ def _declare(l):
         getattr(l, name).restype = i
 
 
-EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_symm_alloc', 'fga_symm_export',
+EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 'fga_symm_alloc', 'fga_symm_export',
            'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_barrier', 'fga_gemm_push',
            'fga_gemm_recv', 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
            'fga_bias_grad', 'fga_mx_quantize')

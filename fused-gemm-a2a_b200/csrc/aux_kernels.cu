@@ -54,7 +54,7 @@ int launch_barrier(long long* flags, const long long* peer_flags, int rank, int 
                    unsigned long long timeout_ns, cudaStream_t stream) {
   barrier_kernel<<<1, 32, 0, stream>>>(flags, peer_flags, rank, p, bump, counters, count,
                                        epoch_out, status, timeout_ns);
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   return kSuccess;
 }
 
@@ -144,7 +144,7 @@ int launch_copy_rank_rows(const void* const* in, void* const* out, int segments,
   else
     copy_rank_rows_kernel<false><<<grid, threads, 0, stream>>>(
         a, rows_in, rows_out, width, static_cast<const uint16_t*>(bias), head_dim, head_off, segments);
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   return kSuccess;
 }
 
@@ -212,7 +212,7 @@ int launch_bias_grad(const void* dy, long long rows, int width, void* out, int o
   dim3 grid1((width + threads * 8 - 1) / (threads * 8), parts);
   bias_grad_partial_kernel<<<grid1, threads, 0, stream>>>(static_cast<const uint16_t*>(dy), scratch,
                                                           rows, width);
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   dim3 grid2((width + threads - 1) / threads);
   if (out_is_f32)
     bias_grad_finish_kernel<float><<<grid2, threads, 0, stream>>>(scratch, static_cast<float*>(out),
@@ -220,7 +220,7 @@ int launch_bias_grad(const void* dy, long long rows, int width, void* out, int o
   else
     bias_grad_finish_kernel<uint16_t><<<grid2, threads, 0, stream>>>(
         scratch, static_cast<uint16_t*>(out), parts, width, accumulate);
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   return kSuccess;
 }
 
@@ -383,7 +383,7 @@ int launch_mx_quantize(const void* a, long long rows, int k, long long stride_ro
                                                    static_cast<uint8_t*>(sf), rows, k, rp, kp,
                                                    stride_k);
   }
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   return kSuccess;
 }
 

@@ -35,6 +35,14 @@ int cuda_fail(cudaError_t e, const char* what);
     if (_e != cudaSuccess) return ::fga::cuda_fail(_e, #expr); \
   } while (0)
 
+// After every kernel launch: surface launch errors and count the launch (fga_launch_count).
+void count_launch();
+#define FGA_LAUNCHED()                   \
+  do {                                   \
+    FGA_CUDA(cudaGetLastError());        \
+    ::fga::count_launch();               \
+  } while (0)
+
 #define FGA_REQUIRE(cond, ...)                                                \
   do {                                                                        \
     if (!(cond)) return ::fga::set_error(::fga::kInvalidArgument, __VA_ARGS__); \

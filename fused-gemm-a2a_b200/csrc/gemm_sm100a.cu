@@ -73,7 +73,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   const long long tiles = static_cast<long long>(P.m_tiles) * P.n_tiles;
   if (P.mode != kRecv && tiles < pairs) pairs = static_cast<int>(tiles);
   ulysses_gemm_kernel<<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, P);
-  FGA_CUDA(cudaGetLastError());
+  FGA_LAUNCHED();
   return kSuccess;
 }
 

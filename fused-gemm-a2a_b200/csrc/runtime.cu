@@ -24,6 +24,9 @@ int cuda_fail(cudaError_t e, const char* what) {
   return set_error(kCudaError, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
 int sm_count() {
   constexpr int kMaxDevices = 64;
   static int cached[kMaxDevices];  // 0 = not queried yet
@@ -83,6 +86,7 @@ extern "C" {
 int fga_version(void) { return 1; }
 const char* fga_last_error(void) { return g_error; }
 int fga_sm_count(void) { return sm_count(); }
+uint64_t fga_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
 
 int fga_symm_alloc(size_t bytes, void** ptr) {
   FGA_REQUIRE(ptr != nullptr && bytes > 0, "fga_symm_alloc: need a size and an output pointer");

@@ -48,6 +48,8 @@ int fga_version(void);
 const char* fga_last_error(void);
 /* Number of SMs of the current device (grid sizing, also used by the host layer). */
 int fga_sm_count(void);
+/* Kernels this library has launched in this process so far (all entry points, all threads). */
+uint64_t fga_launch_count(void);
 
 /* ---- symmetric memory ---------------------------------------------------------------------
  * Replaces torch symmetric memory with the NVSHMEM backend, used by the reference only to

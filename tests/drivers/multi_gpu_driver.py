@@ -1,0 +1,165 @@
+"""Multi-GPU parity driver (one process per GPU, launched by torch.distributed.run).
+
+Every rank runs the public modules on its own GPU; inputs of all ranks are gathered so that each
+rank can evaluate the CPU oracle for the whole CP group and compare its own outputs, gradients and
+the raw transport buffers. Exits non-zero on any mismatch or device-side timeout.
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+for path in (ROOT, os.path.join(ROOT, 'fused-gemm-a2a_b200')):
+    if path not in sys.path:
+        sys.path.insert(0, path)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from fused_gemm_a2a import FusedGemmA2AWorkspace, FusedOutputProjection, FusedQKVProjection  # noqa: E402
+from oracle.ulysses_oracle import UlyssesOracle  # noqa: E402
+
+BF = torch.bfloat16
+
+
+def close(actual, expected, what):
+    actual, expected = actual.detach().float().cpu(), expected.detach().float().cpu()
+    assert actual.shape == expected.shape, f'{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}'
+    scale = expected.abs().max().clamp_min(1e-6)
+    assert (actual - expected).abs().max() <= 1e-2 * scale, f'{what}: max error'
+    assert torch.linalg.norm(actual - expected) <= 2e-3 * torch.linalg.norm(expected) + 1e-6, f'{what}: Frobenius'
+
+
+def gather(t):
+    parts = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, t.contiguous())
+    return [p.cpu() for p in parts]
+
+
+def main():
+    local = int(os.environ['LOCAL_RANK'])
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    dist.init_process_group('nccl', device_id=dev)
+    rank, p = dist.get_rank(), dist.get_world_size()
+    hidden, heads = 1024, 8
+    d = hidden // heads
+    checks = 0
+    for gate, with_bias, bias_in_gemm in ((False, False, False), (True, True, False), (False, True, True)):
+        segments = 4 if gate else 3
+        g = torch.Generator().manual_seed(4321)  # replicated parameters
+        wq = (torch.randn(segments * hidden, hidden, generator=g) / 32).to(BF)
+        wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+        bq = torch.randn(segments * hidden, generator=g).mul(0.5).to(BF) if with_bias else None
+        bo = torch.randn(hidden, generator=g).mul(0.5).to(BF) if with_bias else None
+        ws = FusedGemmA2AWorkspace(hidden, heads, 600, gate=gate)
+        wq_d, wo_d = wq.to(dev).requires_grad_(), wo.to(dev).requires_grad_()
+        bq_d = bq.to(dev).requires_grad_() if with_bias else None
+        bo_d = bo.to(dev).requires_grad_() if with_bias else None
+        qkv = FusedQKVProjection(hidden, heads, weight=wq_d, bias=bq_d, gate=gate, bias_in_gemm=bias_in_gemm)
+        proj = FusedOutputProjection(hidden, heads, weight=wo_d, bias=bo_d)
+        oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, bias_in_gemm=bias_in_gemm)
+        for tokens in (300, 129, 1, 512, 255):
+            g = torch.Generator().manual_seed(1000 * tokens + rank)
+            x = torch.randn(tokens, hidden, generator=g).to(BF).to(dev).requires_grad_()
+            grads = [torch.randn(p * tokens, heads // p, d, generator=g).to(BF).to(dev) for _ in range(segments)]
+            o = torch.randn(p * tokens, heads // p, d, generator=g).to(BF).to(dev).requires_grad_()
+            dy = torch.randn(tokens, hidden, generator=g).to(BF).to(dev)
+            outs = qkv(x, ws)
+            dx, dwq, *dbq = torch.autograd.grad(outs, [x, wq_d] + ([bq_d] if with_bias else []), grads)
+            y = proj(o, ws)
+            do, dwo, *dbo = torch.autograd.grad(y, [o, wo_d] + ([bo_d] if with_bias else []), dy)
+            torch.cuda.synchronize()
+            ws.comm.check_status()
+            # exact transport: the QKV receive buffer still holds this rank's dY, the output receive
+            # buffer this rank's sequence-side O, pad rows zero
+            all_grads = list(zip(*[gather(t) for t in grads]))       # [rank][segment]
+            all_o = gather(o.detach())
+            cap = ws._view(tokens, segments).capacity
+            want_dy = oracle.qkv_recv_buffer(all_grads, rank, cap)
+            assert torch.equal(ws._view(tokens, segments).recv.cpu(), want_dy), 'QKV dgrad transport'
+            assert torch.equal(ws._view(tokens, 1).recv.cpu(), oracle.out_recv_buffer(all_o, rank, cap)), 'output transport'
+            xs, dys = gather(x.detach()), gather(dy)
+            want_outs = oracle.qkv_forward(xs)[rank]
+            for name, got, want in zip('qkvg', outs, want_outs):
+                close(got, want, f'{name} tokens={tokens}')
+            rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
+            close(dx, rdx, 'dx')
+            close(dwq, rdw, 'dW_qkv')
+            close(y, oracle.out_forward(all_o)[rank], 'y')
+            rdos, rparams = oracle.out_backward(all_o, dys)
+            close(do, rdos[rank], 'dO')
+            close(dwo, rparams[rank][0], 'dW_o')
+            if with_bias:
+                close(dbq[0], rdb, 'dbias_qkv')
+                close(dbo[0], rparams[rank][1], 'dbias_o')
+            checks += 1
+        if rank == 0:
+            print(f'PASS gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm}', flush=True)
+
+    # CUDA graph: one captured step replayed with changed inputs
+    tokens, segments = 333, 3
+    ws = FusedGemmA2AWorkspace(hidden, heads, 600)
+    sx = torch.zeros(tokens, hidden, dtype=BF, device=dev).requires_grad_()
+    so = torch.zeros(p * tokens, heads // p, d, dtype=BF, device=dev).requires_grad_()
+    sg = [torch.zeros(p * tokens, heads // p, d, dtype=BF, device=dev) for _ in range(3)]
+    sdy = torch.zeros(tokens, hidden, dtype=BF, device=dev)
+    g = torch.Generator().manual_seed(4321)
+    wq = (torch.randn(3 * hidden, hidden, generator=g) / 32).to(BF)
+    wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+    wq_d, wo_d = wq.to(dev).requires_grad_(), wo.to(dev).requires_grad_()
+    qkv = FusedQKVProjection(hidden, heads, weight=wq_d)
+    proj = FusedOutputProjection(hidden, heads, weight=wo_d)
+    oracle = UlyssesOracle(p, hidden, heads, 3, wq, None, wo, None)
+
+    def step():
+        qs = qkv(sx, ws)
+        dx, dw = torch.autograd.grad(qs, [sx, wq_d], sg)
+        y = proj(so, ws)
+        do, dwo = torch.autograd.grad(y, [so, wo_d], sdy)
+        return (*qs, dx, dw, y, do, dwo)
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        step()
+    stream.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        outputs = step()
+    torch.cuda.current_stream().wait_stream(stream)
+    dist.barrier()
+    for replay in range(3):
+        g = torch.Generator().manual_seed(77 * replay + rank)
+        with torch.no_grad():
+            sx.copy_(torch.randn(sx.shape, generator=g).to(BF))
+            so.copy_(torch.randn(so.shape, generator=g).to(BF))
+            sdy.copy_(torch.randn(sdy.shape, generator=g).to(BF))
+            for t in sg:
+                t.copy_(torch.randn(t.shape, generator=g).to(BF))
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph.replay()
+        torch.cuda.synchronize()
+        ws.comm.check_status()
+        xs, all_o, dys = gather(sx.detach()), gather(so.detach()), gather(sdy)
+        all_grads = list(zip(*[gather(t) for t in sg]))
+        q, k, v, dx, dw, y, do, dwo = outputs
+        for got, want in zip((q, k, v), oracle.qkv_forward(xs)[rank]):
+            close(got, want, f'replay {replay} qkv')
+        rdx, rdw, _ = oracle.qkv_backward(xs, all_grads)[rank]
+        close(dx, rdx, 'replay dx')
+        close(dw, rdw, 'replay dW_qkv')
+        close(y, oracle.out_forward(all_o)[rank], 'replay y')
+        rdos, rparams = oracle.out_backward(all_o, dys)
+        close(do, rdos[rank], 'replay dO')
+        close(dwo, rparams[rank][0], 'replay dW_o')
+    if rank == 0:
+        print(f'PASS cuda graph replay; {checks} eager configurations checked on {p} GPUs', flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,24 @@
+"""Real multi-GPU parity: one process per GPU over NVLink, all the GPUs of the box (2, 4 or 8)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs at least two GPUs')
+def test_fused_modules_across_gpus(native):
+    world = min(8, 1 << (torch.cuda.device_count().bit_length() - 1))
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0', FGA_TIMEOUT_S='10')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={world}',
+           '--master-addr', '127.0.0.1', '--master-port', '29577',
+           os.path.join(ROOT, 'tests', 'drivers', 'multi_gpu_driver.py')]
+    result = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    sys.stdout.write(result.stdout[-4000:])
+    sys.stderr.write(result.stderr[-4000:])
+    assert result.returncode == 0
+    assert 'PASS cuda graph replay' in result.stdout
