@@ -52,6 +52,10 @@ def parse_args():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer measurement')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--cpu-sample-tokens', type=int, default=2048)
+    ap.add_argument('--kernel-case', default=None, choices=('gemm_nt', 'gemm_nn', 'wgrad', 'step'),
+                    help='run only a few launches of one kernel on a small case (for an ncu capture) and exit')
+    ap.add_argument('--case-tokens', type=int, default=8192, help='rows of the --kernel-case problem')
+    ap.add_argument('--case-launches', type=int, default=3)
     return ap.parse_args()
 
 
@@ -412,15 +416,19 @@ def run_gpu_arm(args):
     roofline = None
     if args.impl == 'fused':
         peak, peak_source = measured_peaks()
-        records = []
+        records, others = [], []
 
-        def timed(fn, algorithmic_flops):
+        def timed(fn, label, algorithmic_flops=None):
             def wrapper(*a, **kw):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 out = fn(*a, **kw)
                 e1.record()
-                records.append((e0, e1, algorithmic_flops(*a, **kw)))
+                name = label(*a, **kw) if callable(label) else label
+                if algorithmic_flops is None:
+                    others.append((name, e0, e1))
+                else:
+                    records.append((name, e0, e1, algorithmic_flops(*a, **kw)))
                 return out
             return wrapper
 
@@ -428,17 +436,26 @@ def run_gpu_arm(args):
             # algorithmic rows only: pad rows of the capacity are not counted
             return 2.0 * m * b.shape[0] * b.shape[1]
 
+        def gemm_label(mode, a, b, b_is_kn, c, *rest, **kw):
+            return f'gemm_{mode}[{m}x{b.shape[1] if not b_is_kn else b.shape[0]}->{b.shape[0] if not b_is_kn else b.shape[1]}]'
+
         comm = ws.comm
-        orig_gemm, orig_wgrad = comm.gemm, fused.bf16_wgrad
-        comm.gemm = timed(orig_gemm, gemm_flops)
-        fused.bf16_wgrad = timed(orig_wgrad, lambda dyv, xv, out, status, **kw: 2.0 * dyv.shape[0] * dyv.shape[1] * xv.shape[1])
+        saved = (comm.gemm, fused.bf16_wgrad, comm.barrier, fused.resize_rank_rows)
+        comm.gemm = timed(saved[0], gemm_label, gemm_flops)
+        fused.bf16_wgrad = timed(saved[1], lambda dyv, xv, *a, **kw: f'gemm_wgrad[{dyv.shape[1]}x{xv.shape[1]},k={dyv.shape[0]}]',
+                                 lambda dyv, xv, *a, **kw: 2.0 * dyv.shape[0] * dyv.shape[1] * xv.shape[1])
+        comm.barrier = timed(saved[2], 'barrier')
+        fused.resize_rank_rows = timed(saved[3], 'copy_rank_rows')
         extra = 2
         for _ in range(extra):
             step()
         torch.cuda.synchronize()
-        comm.gemm, fused.bf16_wgrad = orig_gemm, orig_wgrad
-        gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in records)
-        gemm_flops_total = sum(f for _, _, f in records)
+        comm.gemm, fused.bf16_wgrad, comm.barrier, fused.resize_rank_rows = saved
+        gemm_ms = sum(e0.elapsed_time(e1) for _, e0, e1, _ in records)
+        gemm_flops_total = sum(f for *_, f in records)
+        per_launch = [dict(op=name, ms=e0.elapsed_time(e1), tflops=f / e0.elapsed_time(e1) / 1e9)
+                      for name, e0, e1, f in records[len(records) // 2:]]
+        per_launch += [dict(op=name, ms=e0.elapsed_time(e1)) for name, e0, e1 in others[len(others) // 2:]]
         gemm_ms, = max_over_ranks([gemm_ms])
         achieved = gemm_flops_total / (gemm_ms * 1e-3) / 1e12
         a2a_bytes = 2.0 * m * (segments + 1) * hidden * 2 * (p - 1) / p  # both directions' payload per step
@@ -447,7 +464,8 @@ def run_gpu_arm(args):
                         launches_timed=len(records), avg_launch_ms=gemm_ms / max(1, len(records)),
                         gemm_share_of_step=gemm_ms / extra / ms_per_step,
                         frac_of_nominal_2250=achieved / NOMINAL_BF16_TFLOPS,
-                        link_bound_ms_per_step=a2a_bytes / (LINK_GBS * 1e9) * 1e3)
+                        link_bound_ms_per_step=a2a_bytes / (LINK_GBS * 1e9) * 1e3,
+                        launches_rank0_last_step=per_launch)
 
     # ---- end to end: pinned host inputs -> device (prefetched on a copy stream) -> step -> scalar back
     e2e = None
@@ -531,9 +549,82 @@ def run_gpu_arm(args):
     dist.barrier()
 
 
+def run_kernel_case(args):
+    """A few launches of one kernel on a small problem whose operands exceed L2, for profiler
+    captures (`ncu -k regex:ulysses_gemm -c 1 ... python bench.py --kernel-case gemm_nt`). Prints the
+    CUDA-event time per launch; numbers printed under a profiler are not benchmark values."""
+    import torch
+    import build_native
+    build_native.build()
+    import _fga_native
+    lib = _fga_native.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device('cuda', 0)
+    m, h = args.case_tokens, args.hidden
+    bf = torch.bfloat16
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    timeout = 10_000_000_000
+    if args.kernel_case == 'step':
+        import torch.distributed as dist
+        init_distributed(torch, dist)
+        import fused_gemm_a2a as fused
+        ws = fused.FusedGemmA2AWorkspace(h, args.heads, m)
+        wq = (torch.randn(3 * h, h, device=dev) / 64).to(bf).requires_grad_()
+        wo = (torch.randn(h, h, device=dev) / 64).to(bf).requires_grad_()
+        qkv = fused.FusedQKVProjection(h, args.heads, weight=wq)
+        proj = fused.FusedOutputProjection(h, args.heads, weight=wo)
+        x = torch.randn(m, h, device=dev).to(bf).requires_grad_()
+        o = torch.randn(m, args.heads, h // args.heads, device=dev).to(bf).requires_grad_()
+        grads = [torch.randn(m, args.heads, h // args.heads, device=dev).to(bf) for _ in range(3)]
+        dy = torch.randn(m, h, device=dev).to(bf)
+
+        def launch():
+            torch.autograd.grad(qkv(x, ws), [x, wq], grads)
+            torch.autograd.grad(proj(o, ws), [o, wo], dy)
+        flops = flops_per_step(m, h, 3)['total']
+    else:
+        n = 3 * h if args.kernel_case != 'wgrad' else h
+        a = torch.randn(m, h, device=dev).to(bf)
+        if args.kernel_case == 'gemm_nt':      # forward: x [M,K] * W[N,K]^T
+            b, c, call = torch.randn(n, h, device=dev).to(bf), torch.empty(m, n, dtype=bf, device=dev), None
+            call = lambda: lib.fga_gemm_local(a.data_ptr(), 0, b.data_ptr(), 0, m, n, h, h, h, c.data_ptr(), n, 0, 0,  # noqa: E731
+                                              status.data_ptr(), timeout, stream)
+            flops = 2.0 * m * n * h
+        elif args.kernel_case == 'gemm_nn':    # dgrad: dY [M,K=3H] * W[K,N=H]
+            dyv, w = torch.randn(m, n, device=dev).to(bf), torch.randn(n, h, device=dev).to(bf)
+            c = torch.empty(m, h, dtype=bf, device=dev)
+            call = lambda: lib.fga_gemm_local(dyv.data_ptr(), 0, w.data_ptr(), 1, m, h, n, n, h, c.data_ptr(), h, 0, 0,  # noqa: E731
+                                              status.data_ptr(), timeout, stream)
+            flops = 2.0 * m * n * h
+        else:                                  # wgrad: dY[T,N]^T * X[T,K] accumulated in FP32
+            n = 3 * h
+            dyv = torch.randn(m, n, device=dev).to(bf)
+            c = torch.zeros(n, h, dtype=torch.float32, device=dev)
+            call = lambda: lib.fga_gemm_local(dyv.data_ptr(), 1, a.data_ptr(), 1, n, h, m, n, h, c.data_ptr(), h, 1, 1,  # noqa: E731
+                                              status.data_ptr(), timeout, stream)
+            flops = 2.0 * m * n * h
+
+        def launch():
+            _fga_native.check(call())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launch()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.case_launches):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.case_launches
+    print(json.dumps(dict(kernel_case=args.kernel_case, tokens=m, hidden=h, ms_per_launch=ms,
+                          tflops=flops / ms / 1e9, status=status.tolist())), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == 'reference':
+    if args.kernel_case:
+        run_kernel_case(args)
+    elif args.impl == 'reference':
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
