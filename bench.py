@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument('--bias', action='store_true')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer measurement')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-graphs', action='store_true', help='launch eagerly instead of replaying CUDA graphs')
     ap.add_argument('--cpu-sample-tokens', type=int, default=2048)
     ap.add_argument('--kernel-case', default=None, choices=('gemm_nt', 'gemm_nn', 'wgrad', 'step'),
                     help='run only a few launches of one kernel on a small case (for an ncu capture) and exit')
@@ -292,6 +293,11 @@ def run_gpu_arm(args):
     if args.tokens % world or args.heads % world:
         raise SystemExit('tokens and heads must divide over the ranks')
     dev = torch.device('cuda', local)
+    # Everything runs on one non-default stream from the start: autograd ties the gradient
+    # accumulation nodes of the leaves to the stream of their first use, and a node tied to the
+    # legacy default stream cannot take part in a stream capture.
+    work_stream = torch.cuda.Stream()
+    torch.cuda.set_stream(work_stream)
     p, hidden, heads = world, args.hidden, args.heads
     d, m, segments = hidden // heads, args.tokens // world, 4 if args.gate else 3
     bf = torch.bfloat16
@@ -370,11 +376,13 @@ def run_gpu_arm(args):
     state, fns = passes()
     names = ('qkv_fwd', 'qkv_bwd', 'out_fwd', 'out_bwd')
 
-    def step(events=None):
+    def eager_step(events=None):
         for i, fn in enumerate(fns):
             fn()
             if events is not None:
                 events[i + 1].record()
+
+    step = eager_step
 
     def fence():
         torch.cuda.synchronize()
@@ -389,12 +397,41 @@ def run_gpu_arm(args):
     # ---- device-resident measurement (the clock sampler starts before the warm-up so that it is
     # already streaming when the timed region begins)
     marks = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    graph_note = 'eager launches'
     with ClockSampler(local) as clocks:
         for _ in range(max(args.warmup, 3)):
-            step()
+            eager_step()
         fence()
         if args.impl == 'fused':
             ws.comm.check_status()
+        launches_per_step = None
+        if not args.no_graphs:
+            # One CUDA graph per pass (shared memory pool), replayed back to back: launch latency of
+            # the host is out of the measurement, as in the reference's graph-captured benchmark.
+            side = work_stream
+            try:
+                fence()
+                graphs, pool, before = [], None, launches()
+                for fn in fns:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool, stream=side, capture_error_mode='thread_local'):
+                        fn()
+                    pool = pool or g.pool()
+                    graphs.append(g)
+                launches_per_step = launches() - before
+                def step(events=None):
+                    for i, g in enumerate(graphs):
+                        g.replay()
+                        if events is not None:
+                            events[i + 1].record()
+                graph_note = 'one CUDA graph per pass, replayed'
+            except Exception as error:  # capture not supported for this arm: stay eager, say so
+                graph_note = f'eager launches (graph capture failed: {type(error).__name__}: {str(error)[:300]})'
+                step = eager_step
+            fence()
+            for _ in range(2):
+                step()
+            fence()
         launches_before = launches()
         clocks.begin()
         for k in range(args.steps):
@@ -403,6 +440,8 @@ def run_gpu_arm(args):
         fence()
         clocks.end()
     gpu_launches = launches() - launches_before
+    if launches_per_step is not None and step is not eager_step:
+        gpu_launches = launches_per_step * args.steps  # replayed launches are not seen by the counter
     total_ms = marks[0][0].elapsed_time(marks[-1][4])
     pass_ms = [sum(marks[k][i].elapsed_time(marks[k][i + 1]) for k in range(args.steps)) / args.steps
                for i in range(4)]
@@ -448,7 +487,7 @@ def run_gpu_arm(args):
         fused.resize_rank_rows = timed(saved[3], 'copy_rank_rows')
         extra = 2
         for _ in range(extra):
-            step()
+            eager_step()
         torch.cuda.synchronize()
         comm.gemm, fused.bf16_wgrad, comm.barrier, fused.resize_rank_rows = saved
         gemm_ms = sum(e0.elapsed_time(e1) for _, e0, e1, _ in records)
@@ -532,7 +571,7 @@ def run_gpu_arm(args):
         config=dict(workload=f'{args.tokens} total tokens, H={hidden}, {heads}x{d} heads, CP={world} '
                              f'(M={m} per rank), QKV{"G" if args.gate else ""} + output projection, forward + dgrad + wgrad'
                              f'{", bias" if args.bias else ", no bias"}',
-                    parallelism=f'cp{world}', l2='inputs larger than L2 (no flush needed)'),
+                    parallelism=f'cp{world}', l2='inputs larger than L2 (no flush needed)', launch=graph_note),
         tflops_per_gpu=per_gpu_tflops, pct_of_nominal_2250=100 * per_gpu_tflops / NOMINAL_BF16_TFLOPS,
         passes={n: dict(ms=ms, tflops_per_gpu=flops[n] / (ms * 1e-3) / 1e12) for n, ms in zip(names, pass_ms)},
         step_roofline=dict(compute_ms_at_2250=flops['total'] / NOMINAL_BF16_TFLOPS / 1e9,
