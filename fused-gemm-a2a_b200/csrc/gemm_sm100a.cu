@@ -64,8 +64,9 @@ static int encode_operand(CUtensorMap* map, const void* base, int mn_major, long
   return encode_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, rows, pitch, 64, 64);
 }
 
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& P,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cudaStream_t stream) {
+  const int forced_stages = env_int("FGA_STAGES", 0);  // tuning knob: fewer pipeline stages
+  if (forced_stages >= 2 && forced_stages <= P.stages) P.stages = forced_stages;
   const int threads = 32 * (kGemmWarps + (P.mode == kRecv ? kPusherWarps : 0));
   int pairs = 0;
   const int rc = resident_pairs(threads, &pairs);
@@ -106,6 +107,7 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
   P.n_tiles = n / P.bn;
   P.k_tiles = (k + kTileK - 1) / kTileK;
   P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
+  P.stages = kMaxStages;
   P.a_mn = 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
@@ -146,7 +148,10 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   FGA_REQUIRE(n >= 128 && n % 128 == 0, "GEMM mode must be push/recv and tile N must divide output width");
   FGA_REQUIRE(split >= 1 && 128 % split == 0, "FUSED_PUSH_SPLIT must divide 128");
   FGA_REQUIRE((roles & 3) != 0 && (roles & ~3) == 0, "fga_gemm_recv: roles is a mask of 1 (GEMM) and 2 (pushers)");
-  for (int t = 0; t < num_in; ++t) FGA_REQUIRE(srcs[t], "fga_gemm_recv: null source %d", t);
+  for (int t = 0; t < num_in; ++t)
+    FGA_REQUIRE(srcs[t] && reinterpret_cast<uintptr_t>(srcs[t]) % 16 == 0,
+                "fga_gemm_recv: source %d must be a 16-byte aligned device pointer", t);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv: output must be 16-byte aligned");
   GemmParams P{};
   P.mode = kRecv;
   P.epi = kEpiBf16;
@@ -155,6 +160,19 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   P.n_tiles = n / P.bn;
   P.k_tiles = k / kTileK;
   P.group_m = env_int("FGA_GROUP_M_RECV", 4);
+  P.stages = kMaxStages - 1;  // the sixth stage's shared memory holds the pusher buffers
+  {
+    // Pusher chunking: a chunk is `push_rows` rows of `push_units` 256-byte head units, at most
+    // one 4 KiB buffer. Rows wider than a buffer are cut into equal pieces of whole units.
+    const int hpr = k / (p * num_in * 128), sub_rows = 128 / split;
+    int units = hpr;
+    while (units > kPushBufBytes / 256 || hpr % units) --units;
+    int rows = 1;
+    if (units == hpr)
+      while (rows * 2 * units * 256 <= kPushBufBytes && rows * 2 <= sub_rows) rows *= 2;
+    P.push_units = units;
+    P.push_rows = rows;
+  }
   P.a_mn = 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
@@ -203,6 +221,7 @@ int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m
   P.n_tiles = n / P.bn;
   P.k_tiles = (k + kTileK - 1) / kTileK;
   P.group_m = env_int("FGA_GROUP_M_LOCAL", 8);
+  P.stages = kMaxStages;
   P.a_mn = a_is_km ? 1 : 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);

@@ -4,36 +4,43 @@
 //   local : C = A * B^T, plain store or FP32 accumulate (weight gradients)
 //   push  : the epilogue stores every finished 128x128 head tile straight into the owning peer's
 //           head-side buffer over NVLink (QKV forward, output-projection dgrad)
-//   recv  : pusher warps copy this rank's head-side input into the peers' receive buffers and
-//           bump per-row-block arrival counters; the TMA producer polls its own counters before
-//           loading a row block (output-projection forward, QKV dgrad)
+//   recv  : pusher warps move this rank's head-side input into the peers' receive buffers with
+//           bulk copies (global -> shared -> peer global) and bump per-row-block arrival counters;
+//           the TMA producer polls its own counters before loading a row block
+//           (output-projection forward, QKV dgrad)
 //
 // Layout of one CTA pair (cluster 2x1x1): the pair owns a 256 x BN output tile, each CTA 128 rows.
 // Each CTA TMA-loads its own 128 rows of A and its half (BN/2) of B per 64-wide K step; one thread
 // of the leader CTA issues tcgen05.mma.cta_group::2 into TMEM of both CTAs (2 accumulator stages
 // of BN columns each). Four epilogue warps per CTA read TMEM (thread = row), convert, write their
-// own row segment to shared memory and ship it with a 1-D bulk copy (cp.async.bulk) to local or
-// peer global memory; FP32 gradient accumulation uses the bulk reduce-add. No TMA load uses
-// cluster multicast. Every wait is bounded: on expiry the waiter records an error in the caller's
-// status word, all roles drain, TMEM is freed and the kernel returns.
+// own 128-byte row piece to shared memory and ship it with a 1-D bulk copy (cp.async.bulk) to
+// local or peer global memory; FP32 gradient accumulation uses the bulk reduce-add. No TMA load
+// uses cluster multicast. Every wait is bounded: on expiry the waiter records an error in the
+// caller's status word, all roles drain, TMEM is freed and the kernel returns.
+//
+// Shared memory (215 KiB): local/push run 6 pipeline stages of 32 KiB; recv runs 5 stages and
+// gives the sixth to the pusher warps (4 warps x 2 buffers x 4 KiB); 18 KiB of epilogue staging.
 #pragma once
 #include "ptx.cuh"
 #include "common.cuh"
 
 namespace fga {
 
-constexpr int kStages = 5;
+constexpr int kMaxStages = 6;
 constexpr int kTileM = 128;             // rows per CTA
 constexpr int kTileK = 64;              // BF16 elements per K step (128 bytes = one swizzle span)
 constexpr int kABytes = kTileM * 128;   // 16 KiB
 constexpr int kBBytes = 128 * 128;      // 16 KiB (BN/2 <= 128 rows)
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSlotPitch = 272;         // per-thread staging row: 256 B payload + 16 B skew
+constexpr int kPieceBytes = 128;        // epilogue row piece: 64 BF16 or 32 FP32 columns
+constexpr int kSlotPitch = kPieceBytes + 16;  // 16-byte skew: conflict-free 16-byte stores
 constexpr int kStagingBytes = 128 * kSlotPitch;
 constexpr int kBarrierBytes = 256;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 constexpr int kGemmWarps = 6;           // TMA, MMA, 4 epilogue
 constexpr int kPusherWarps = 4;
+constexpr int kPushBufBytes = 4096;     // per pusher warp: two of these
+constexpr int kSmemBytes = kMaxStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+static_assert(kPusherWarps * 2 * kPushBufBytes == kStageBytes, "pusher buffers reuse one stage");
 
 enum GemmMode : int { kLocal = 0, kPush = 1, kRecv = 2 };
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Store = 1, kEpiF32Add = 2 };
@@ -42,6 +49,7 @@ struct GemmParams {
   // geometry
   int m_tiles, n_tiles, k_tiles;  // 256-row pair tiles, BN-column tiles, 64-element K steps
   int bn;                         // 128 or 256
+  int stages;                     // pipeline stages in use (<= kMaxStages)
   int group_m;                    // pair tiles per raster group (N varies fastest inside a group)
   int a_mn, b_mn;                 // 1 = operand is MN-major in global memory (transposed read)
   uint32_t idesc;                 // tcgen05 instruction descriptor
@@ -66,6 +74,8 @@ struct GemmParams {
   const long long* peer_counters;  // device int64[P]
   const void* src[4];              // head-side inputs [P*src_rows, heads_per_rank*128] BF16
   int num_in, src_rows, split;
+  int push_units;                  // 256-byte head units per pusher chunk row (divides heads_per_rank)
+  int push_rows;                   // rows per pusher chunk (1 unless push_units == heads_per_rank)
   long long recv_k;                // elements per receive-buffer row
   int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
   // bounded waits
@@ -170,25 +180,31 @@ __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Pusher warps (recv mode). Job = (row block, input segment, destination, row sub-block): copy
+// Pusher warps (recv mode). Job = (row block, input segment, destination, row sub-block): move
 // rows [row0, row0 + 128/split) of this rank's head-side input for destination d into d's receive
 // buffer, columns in Megatron order [head][q|k|v|g][D], rows past src_rows as zeros; then one
-// release-increment of d's counter for that row block.
-// Mirrors fused_gemm_a2a_kernels.py:291-380 (_push_one, _push_jobs).
+// release-increment of d's counter for that row block (fused_gemm_a2a_kernels.py:291-380 is the
+// reference's register-copy version). Here one lane per warp drives the TMA unit: a chunk of up
+// to 4 KiB is bulk-loaded from local memory into one of the warp's two shared buffers and
+// bulk-stored to the peer in 256-byte head units (or whole rows when the columns are contiguous),
+// so the data never passes through registers and remote stores queue in the copy engine.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane) {
+__device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane, uint32_t buf0,
+                                            uint32_t bar0, WaitCtx& w) {
   const int hpr = P.heads_per_rank;
+  const int row_bytes = hpr * 256;
   const int sub_rows = kTileM / P.split;
+  const int upp = P.push_units, rpc = P.push_rows;
+  const int pieces_per_row = hpr / upp;
+  const int chunk_row_bytes = upp * 256;
+  const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
   const int jobs_per_block = P.num_in * P.p * P.split;
-  const int row_blocks = P.m_tiles * 2;
-  const long long num_jobs = static_cast<long long>(row_blocks) * jobs_per_block;
+  const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
   const int worker = blockIdx.x * kPusherWarps + pusher;
   const int workers = gridDim.x * kPusherWarps;
-  const int half = lane >> 4;          // two 256-byte units per pass
-  const int off16 = (lane & 15) * 16;  // byte offset inside a unit
-  const long long src_pitch = static_cast<long long>(hpr) * 256;  // bytes per source row
-  const int units = sub_rows * hpr;
-  for (long long job = worker; job < num_jobs; job += workers) {
+  uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
+  uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
+  for (long long job = worker; job < num_jobs && !w.dead; job += workers) {
     const int mi = static_cast<int>(job / jobs_per_block);
     int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
     const int q = rest % P.split;
@@ -197,79 +213,120 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
     const int t = rest / P.p;
     const int row0 = mi * kTileM + q * sub_rows;
     const char* src = static_cast<const char*>(P.src[t]) +
-                      (static_cast<long long>(d) * P.src_rows + row0) * src_pitch;
+                      (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
     char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
-    for (int base = 0; base < units; base += 16) {
-      uint4 v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int u = base + 2 * i + half;
-        const int r = u / hpr, j = u - r * hpr;
-        v[i] = make_uint4(0, 0, 0, 0);
-        if (u < units && row0 + r < P.src_rows)
-          v[i] = ld_cs_v4(src + r * src_pitch + j * 256 + off16);
+    for (int c = 0; c < chunks_per_job; ++c) {
+      int r0, u0;
+      if (pieces_per_row == 1) {
+        r0 = c * rpc;
+        u0 = 0;
+      } else {
+        r0 = c / pieces_per_row;
+        u0 = (c - r0 * pieces_per_row) * upp;
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int u = base + 2 * i + half;
-        const int r = u / hpr, j = u - r * hpr;
-        if (u < units) {
-          const long long col = (static_cast<long long>(P.rank * hpr + j) * P.num_in + t) * 128;
-          st_cs_v4(dst + (static_cast<long long>(r) * P.recv_k + col) * 2 + off16, v[i]);
+      const int b = issued & 1;
+      const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
+      const int valid = max(0, min(rpc, P.src_rows - (row0 + r0)));  // rows that exist in the source
+      if (lane == 0) bulk_wait_read<1>();  // the group that used this buffer last has left shared memory
+      __syncwarp();
+      if (lane == 0 && valid > 0) {
+        mbar_arrive_expect_tx(bar, valid * chunk_row_bytes);
+        bulk_load(buf, src + static_cast<long long>(r0) * row_bytes + u0 * 256, valid * chunk_row_bytes, bar);
+      }
+      if (valid < rpc) {  // rows beyond the logical count travel as exact zeros
+        for (int o = valid * chunk_row_bytes + lane * 16; o < rpc * chunk_row_bytes; o += 512)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(buf + o), "r"(0u) : "memory");
+        fence_proxy_async_shared();
+      }
+      __syncwarp();
+      if (lane == 0) {
+        bool ok = true;
+        if (valid > 0) {
+          ok = mbar_wait(bar, loads[b] & 1, w, 40);
+          ++loads[b];
         }
+        if (ok) {
+          for (int r = 0; r < rpc; ++r) {
+            char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
+            if (P.num_in == 1) {
+              bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
+                         chunk_row_bytes);
+            } else {
+              for (int u = 0; u < upp; ++u) {
+                const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
+                bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
+              }
+            }
+          }
+        }
+        bulk_commit();
       }
+      ++issued;
     }
-    // The warp barrier orders every lane's stores before lane 0's release, which is cumulative.
-    __syncwarp();
-    if (lane == 0) red_release_sys_add(reinterpret_cast<int*>(P.peer_counters[d]) + mi, 1);
+    if (lane == 0) {
+      // All of this job's bulk stores have been performed; the release makes them visible to
+      // whoever acquires the counter.
+      bulk_wait_all();
+      fence_proxy_async_all();
+      if (!w.dead) red_release_sys_add(reinterpret_cast<int*>(P.peer_counters[d]) + mi, 1);
+    }
+    w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
   }
+  if (lane == 0) bulk_wait_all();
 }
 
 // ---------------------------------------------------------------------------------------------
-// Epilogue for one 128-row x BN accumulator of this CTA. Thread = output row.
+// Epilogue for one 128-row x BN accumulator of this CTA. Thread = output row; the row leaves in
+// 128-byte pieces (64 BF16 or 32 FP32 columns), each staged in the thread's own shared slot and
+// shipped with one bulk copy, so no thread ever waits for another.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem_acc, int quarter,
                                               int lane, uint32_t slot, int row, int b_row0,
                                               uint32_t tempty_leader, bool& stores_pending) {
   const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-  if (P.epi == kEpiBf16) {
-    const int halves = P.bn >> 7;
-    for (int h = 0; h < halves; ++h) {
-      // Destination of this row's 256-byte segment.
-      char* dst = nullptr;
-      const int unit = (b_row0 >> 7) + h;  // 128-wide head tile index in weight-row order
-      if (P.mode == kPush) {
-        const int head = unit / P.segments, seg = unit - head * P.segments;
-        const int dest = head / P.heads_per_rank, within = head - dest * P.heads_per_rank;
-        dst = reinterpret_cast<char*>(P.peer_heads[seg][dest]) +
-              ((static_cast<long long>(P.rank) * P.head_rows + row) * P.head_pitch + within * 128) * 2;
-      } else if (row < P.c_rows) {
-        dst = static_cast<char*>(P.c) + (static_cast<long long>(row) * P.c_pitch + unit * 128) * 2;
-      }
-      if (stores_pending) bulk_wait_read_all();
+  const bool bf16_out = P.epi == kEpiBf16;
+  const int piece_cols = bf16_out ? 64 : 32;
+  const int chunks = piece_cols >> 5;
+  const int pieces = P.bn / piece_cols;
+  for (int pc = 0; pc < pieces; ++pc) {
+    const int col0 = pc * piece_cols;
+    char* dst = nullptr;
+    if (P.mode == kPush) {
+      const int unit = (b_row0 + col0) >> 7;  // 128-wide head tile in weight-row order
+      const int head = unit / P.segments, seg = unit - head * P.segments;
+      const int dest = head / P.heads_per_rank, within = head - dest * P.heads_per_rank;
+      dst = reinterpret_cast<char*>(P.peer_heads[seg][dest]) +
+            ((static_cast<long long>(P.rank) * P.head_rows + row) * P.head_pitch + within * 128 +
+             ((b_row0 + col0) & 127)) * 2;
+    } else if (row < P.c_rows) {
+      dst = static_cast<char*>(P.c) +
+            (static_cast<long long>(row) * P.c_pitch + b_row0 + col0) * (bf16_out ? 2 : 4);
+    }
+    if (stores_pending) bulk_wait_read_all();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + lane_base + h * 128 + c * 32, r);
-        tmem_ld_wait();
-        if (h == halves - 1 && c == 3) {
-          // Last TMEM read of this accumulator stage: hand it back to the MMA thread.
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty_leader);
-        }
+    for (int c = 0; c < chunks; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_acc + lane_base + col0 + c * 32, r);
+      tmem_ld_wait();
+      if (pc == pieces - 1 && c == chunks - 1) {
+        // Last TMEM read of this accumulator stage: hand it back to the MMA thread.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty_leader);
+      }
+      if (bf16_out) {
         if (P.bias != nullptr) {
-          const uint4* bp = reinterpret_cast<const uint4*>(P.bias + b_row0 + h * 128 + c * 32);
+          const uint4* bp = reinterpret_cast<const uint4*>(P.bias + b_row0 + col0 + c * 32);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const uint4 b = __ldg(bp + v);
-            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+            const uint32_t wv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               r[v * 8 + e * 2] = __float_as_uint(__uint_as_float(r[v * 8 + e * 2]) +
-                                                 bf16_bits_to_f32(w[e] & 0xffffu));
+                                                 bf16_bits_to_f32(wv[e] & 0xffffu));
               r[v * 8 + e * 2 + 1] = __float_as_uint(__uint_as_float(r[v * 8 + e * 2 + 1]) +
-                                                     bf16_bits_to_f32(w[e] >> 16));
+                                                     bf16_bits_to_f32(wv[e] >> 16));
             }
           }
         }
@@ -283,47 +340,22 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem
                        "r"(a0), "r"(a1), "r"(a2), "r"(a3)
                        : "memory");
         }
-      }
-      fence_proxy_async_shared();
-      if (dst != nullptr) {
-        bulk_store(dst, slot, 256);
-        bulk_commit();
-        stores_pending = true;
-      }
-    }
-  } else {
-    // FP32 output: 64 columns (256 bytes) per piece.
-    const int pieces = P.bn >> 6;
-    for (int s = 0; s < pieces; ++s) {
-      char* dst = nullptr;
-      if (row < P.c_rows)
-        dst = static_cast<char*>(P.c) + (static_cast<long long>(row) * P.c_pitch + b_row0 + s * 64) * 4;
-      if (stores_pending) bulk_wait_read_all();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + lane_base + s * 64 + c * 32, r);
-        tmem_ld_wait();
-        if (s == pieces - 1 && c == 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty_leader);
-        }
+      } else {
 #pragma unroll
         for (int v = 0; v < 8; ++v)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + c * 128 + v * 16),
-                       "r"(r[v * 4]), "r"(r[v * 4 + 1]), "r"(r[v * 4 + 2]), "r"(r[v * 4 + 3])
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot + v * 16), "r"(r[v * 4]),
+                       "r"(r[v * 4 + 1]), "r"(r[v * 4 + 2]), "r"(r[v * 4 + 3])
                        : "memory");
       }
-      fence_proxy_async_shared();
-      if (dst != nullptr) {
-        if (P.epi == kEpiF32Add)
-          bulk_reduce_add_f32(dst, slot, 256);
-        else
-          bulk_store(dst, slot, 256);
-        bulk_commit();
-        stores_pending = true;
-      }
+    }
+    fence_proxy_async_shared();
+    if (dst != nullptr) {
+      if (P.epi == kEpiF32Add)
+        bulk_reduce_add_f32(dst, slot, kPieceBytes);
+      else
+        bulk_store(dst, slot, kPieceBytes);
+      bulk_commit();
+      stores_pending = true;
     }
   }
 }
@@ -337,11 +369,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
                         const __grid_constant__ GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t staging = smem_base + kStages * kStageBytes;
+  const uint32_t push_bufs = smem_base + (kMaxStages - 1) * kStageBytes;  // recv mode: sixth stage
+  const uint32_t staging = smem_base + kMaxStages * kStageBytes;
   const uint32_t bars = staging + kStagingBytes;
-  // barrier layout (8 bytes each): full[kStages], empty[kStages], tfull[2], tempty[2]
-  const uint32_t full0 = bars, empty0 = bars + 8 * kStages, tfull0 = bars + 16 * kStages,
-                 tempty0 = tfull0 + 16, tmem_slot = tempty0 + 16, abort_word = tmem_slot + 8;
+  // barrier layout (8 bytes each): full[6], empty[6], tfull[2], tempty[2], pusher[4][2]
+  const uint32_t full0 = bars, empty0 = bars + 8 * kMaxStages, tfull0 = bars + 16 * kMaxStages,
+                 tempty0 = tfull0 + 16, push_bar0 = tempty0 + 16,
+                 tmem_slot = push_bar0 + 16 * kPusherWarps, abort_word = tmem_slot + 8;
+  static_assert(16 * kMaxStages + 32 + 16 * kPusherWarps + 16 <= kBarrierBytes, "barrier area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -351,11 +386,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   const int pairs = gridDim.x >> 1;
   const int total_tiles = P.m_tiles * P.n_tiles;
   const bool gemm_on = (P.roles & 1) != 0;
+  const int stages = P.stages;
 
   WaitCtx w{P.status, P.timeout_ns, abort_word, false};
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(full0 + 8 * i, 1);   // leader producer's arrive.expect_tx (+ both CTAs' bytes)
       mbar_init(empty0 + 8 * i, 1);  // one tcgen05.commit arrival per use
     }
@@ -363,6 +399,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       mbar_init(tfull0 + 8 * i, 1);   // one tcgen05.commit arrival per tile
       mbar_init(tempty0 + 8 * i, 8);  // 4 epilogue warps x 2 CTAs
     }
+    for (int i = 0; i < 2 * kPusherWarps; ++i) mbar_init(push_bar0 + 8 * i, 1);
     asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_word), "r"(0u) : "memory");
     fence_mbar_init();
   }
@@ -418,7 +455,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
             tma_load_2d_pair(b_dst, &tmap_b, full_leader, b_row0, k0);
             if (b_half > 64) tma_load_2d_pair(b_dst + 8192, &tmap_b, full_leader, b_row0 + 64, k0);
           }
-          if (++s == kStages) {
+          if (++s == stages) {
             s = 0;
             ph ^= 1;
           }
@@ -453,7 +490,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
             mma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, P.idesc,
                           (kt | k) != 0 ? 1u : 0u);
           tc_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs when the MMAs retire
-          if (++s == kStages) {
+          if (++s == stages) {
             s = 0;
             ph ^= 1;
           }
@@ -500,7 +537,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
     }
   } else {
     // ------------------------------------------------------------------ pusher warps (recv mode)
-    if (P.mode == kRecv && (P.roles & 2) != 0) run_pushers(P, warp - kGemmWarps, lane);
+    if (P.mode == kRecv && (P.roles & 2) != 0) {
+      const int pusher = warp - kGemmWarps;
+      run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, w);
+    }
   }
 
   // Teardown: nobody leaves while the pair may still touch this CTA's shared memory or TMEM.
