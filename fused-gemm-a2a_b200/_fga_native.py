@@ -50,17 +50,20 @@ def _declare(l):
     l.fga_bias_grad_scratch_floats.argtypes = [i64, i]
     l.fga_bias_grad_scratch_floats.restype = i64
     l.fga_bias_grad.argtypes = [vp, i64, i, vp, i, i, vp, vp]
+    l.fga_bias_grad_static_capacity_floats.restype = i64
+    l.fga_bias_grad_static.argtypes = [vp, i64, i, vp, i, i, vp]
     l.fga_mx_quantize.argtypes = [vp, i64, i, i64, i64, vp, vp, i64, i, vp]
     for name in ('fga_symm_alloc', 'fga_symm_export', 'fga_symm_open', 'fga_symm_close',
                  'fga_symm_free', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
-                 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_mx_quantize'):
+                 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
+                 'fga_mx_quantize'):
         getattr(l, name).restype = i
 
 
 EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 'fga_symm_alloc', 'fga_symm_export',
            'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_barrier', 'fga_gemm_push',
            'fga_gemm_recv', 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
-           'fga_bias_grad', 'fga_mx_quantize')
+           'fga_bias_grad', 'fga_bias_grad_static_capacity_floats', 'fga_bias_grad_static', 'fga_mx_quantize')
 
 
 def check(rc, exc=FgaError):

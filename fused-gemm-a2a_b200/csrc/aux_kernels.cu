@@ -225,6 +225,54 @@ int launch_bias_grad(const void* dy, long long rows, int width, void* out, int o
 }
 
 // ---------------------------------------------------------------------------------------------
+// Bias gradient without any allocation, for callers that must not (or cannot) allocate device
+// memory when they call: code running under a memory budget that is already fully planned, an
+// allocator-free plugin host, or a call site where a cudaMalloc would serialize the device. The
+// FP32 partial sums live in a fixed array that is part of this library's device image; every GPU
+// that loads the library holds these 4 MiB until the process exits.
+//
+// The array is shared by every call on a device and keeps whatever the previous call left in it.
+// Nothing has to be cleared: pass 1 writes every partial sum that pass 2 reads. Two calls that
+// overlap on the GPU (different streams, or graphs replayed concurrently) race on the array.
+// ---------------------------------------------------------------------------------------------
+constexpr long long kStaticScratchFloats = 1ll << 20;  // 256-row parts x width <= 1 Mi floats (4 MiB)
+static __device__ __align__(256) float g_bias_scratch[kStaticScratchFloats];
+
+long long bias_grad_static_capacity_floats() { return kStaticScratchFloats; }
+
+// Device address of the array for the current device. In host code the symbol is only a stand-in,
+// never a device pointer, so the address is looked up once per device with that device current.
+static int static_scratch_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cached[kMaxDevices];  // null = not looked up yet on that device
+  int dev = 0;
+  FGA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(kUnsupported, "device index %d out of range", dev);
+  if (cached[dev] == nullptr) {
+    float* address = nullptr;
+    FGA_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_bias_scratch));
+    if (address == nullptr) return set_error(kCudaError, "the static scratch array has no device address");
+    cached[dev] = address;
+  }
+  *out = cached[dev];
+  return kSuccess;
+}
+
+int launch_bias_grad_static(const void* dy, long long rows, int width, void* out, int out_is_f32,
+                            int accumulate, cudaStream_t stream) {
+  const long long needed = bias_grad_scratch_floats(rows, width);
+  if (needed > kStaticScratchFloats)
+    return set_error(kInvalidArgument,
+                     "fga_bias_grad_static: %lld rows x %d columns need %lld scratch floats, the built-in "
+                     "array holds %lld; use fga_bias_grad with caller-provided scratch",
+                     rows, width, needed, kStaticScratchFloats);
+  float* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != kSuccess) return rc;
+  return launch_bias_grad(dy, rows, width, out, out_is_f32, accumulate, scratch, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
 // MXFP8 quantizer: E4M3 payload + one E8M0 scale per 32 elements along K.
 // Scale policy (fused_gemm_a2a_kernels.py:1200-1219): e = ceil(log2(amax / 448)) from the FP32
 // exponent/mantissa of amax (448 = 1.75 * 2^8), clamped to [-126, 127]; zero group -> e = 0;

@@ -15,6 +15,9 @@ int launch_copy_rank_rows(const void* const* in, void* const* out, int segments,
 long long bias_grad_scratch_floats(long long rows, int width);
 int launch_bias_grad(const void* dy, long long rows, int width, void* out, int out_is_f32,
                      int accumulate, float* scratch, cudaStream_t stream);
+long long bias_grad_static_capacity_floats();
+int launch_bias_grad_static(const void* dy, long long rows, int width, void* out, int out_is_f32,
+                            int accumulate, cudaStream_t stream);
 
 int launch_mx_quantize(const void* a, long long rows, int k, long long stride_row,
                        long long stride_k, void* q, void* sf, long long rp, int kp,

@@ -171,6 +171,16 @@ int fga_bias_grad(const void* dy, int64_t rows, int width, void* out, int out_is
                           static_cast<cudaStream_t>(stream));
 }
 
+int64_t fga_bias_grad_static_capacity_floats(void) { return bias_grad_static_capacity_floats(); }
+
+int fga_bias_grad_static(const void* dy, int64_t rows, int width, void* out, int out_is_f32,
+                         int accumulate, void* stream) {
+  FGA_REQUIRE(dy && out && rows >= 1 && width >= 1,
+              "Bias reduction requires contiguous BF16 rows and a BF16/FP32 output vector");
+  return launch_bias_grad_static(dy, rows, width, out, out_is_f32, accumulate,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 int fga_mx_quantize(const void* a, int64_t rows, int k, int64_t stride_row, int64_t stride_k,
                     void* q, void* sf, int64_t rows_padded, int k_padded, void* stream) {
   FGA_REQUIRE(a && q && sf && rows >= 1 && k >= 1, "MXFP8 quantization requires a BF16 matrix");

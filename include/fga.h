@@ -120,6 +120,19 @@ int64_t fga_bias_grad_scratch_floats(int64_t rows, int width);
 int fga_bias_grad(const void* dy, int64_t rows, int width, void* out, int out_is_f32,
                   int accumulate, float* scratch, void* stream);
 
+/* No counterpart in the reference. The same reduction as fga_bias_grad for callers that cannot
+ * hand over scratch memory because they must not allocate at the call site (a fully planned
+ * memory budget, a host that forbids cudaMalloc in its hot path): the FP32 partial sums go to a
+ * 4 MiB array that is part of the library's device image, so this call allocates nothing, and
+ * neither does anything it calls. Limit: ceil(rows / 256) * width must not exceed
+ * fga_bias_grad_static_capacity_floats() (1 Mi floats); larger problems are rejected with
+ * FGA_INVALID_ARGUMENT. The first call on each device looks up the array's device address; make
+ * that first call before any stream capture begins. All calls on a device share the array, which
+ * keeps the previous call's partial sums; calls that overlap on the GPU race with each other. */
+int64_t fga_bias_grad_static_capacity_floats(void);
+int fga_bias_grad_static(const void* dy, int64_t rows, int width, void* out, int out_is_f32,
+                         int accumulate, void* stream);
+
 /* Replaces mxfp8_quantize / _mx_quant_kernel (fused_gemm_a2a_kernels.py:1222-1292, 1358-1376).
  * a: BF16 [rows, k] with element strides (stride_row, stride_k), one of them 1. q: E4M3
  * [rows_padded, k_padded]; sf: rows_padded*k_padded/32 E8M0 bytes in the tcgen05 128x4 layout. */
