@@ -43,7 +43,7 @@ def _declare(l):
     l.fga_symm_free.argtypes = [vp]
     l.fga_barrier.argtypes = [vp, vp, i, i, i, vp, i, vp, vp, c_uint64, vp]
     l.fga_gemm_push.argtypes = [vp, i, i, i, vp, i, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
-    l.fga_gemm_recv.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, vp,
+    l.fga_gemm_recv.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, vp, vp, vp,
                                 c_uint64, vp]
     l.fga_gemm_local.argtypes = [vp, i, vp, i, i, i, i, i64, i64, vp, i64, i, i, vp, c_uint64, vp]
     l.fga_copy_rank_rows.argtypes = [pp, pp, i, i, i64, i64, i, vp, i, i, vp]

@@ -135,7 +135,8 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
 int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_is_kn, int n,
                   void* c, const int64_t* peer_recv, const int64_t* peer_counters,
                   int32_t* counters, const void* const* srcs, int num_in, int src_rows, int split,
-                  int rank, int p, int roles, int32_t* status, uint64_t timeout_ns, void* stream) {
+                  int rank, int p, int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
+                  uint64_t timeout_ns, void* stream) {
   FGA_REQUIRE(recv && b && c && peer_recv && peer_counters && counters && srcs && status,
               "fga_gemm_recv: null argument");
   FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_recv: bad rank %d of %d", rank, p);
@@ -193,6 +194,12 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   P.split = split;
   P.recv_k = k;
   P.roles = roles;
+  P.push_warps = env_int("FGA_PUSHER_WARPS", 2);  // warps per CTA that keep pushing after the first groups
+  if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
+  P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
+  P.epoch = reinterpret_cast<const long long*>(epoch);
+  P.progress = progress;
+  P.push_lead = env_int("FGA_PUSH_LEAD", 0);
   P.status = status;
   P.timeout_ns = timeout_ns;
   CUtensorMap ta, tb;

@@ -78,6 +78,11 @@ struct GemmParams {
   int push_rows;                   // rows per pusher chunk (1 unless push_units == heads_per_rank)
   long long recv_k;                // elements per receive-buffer row
   int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
+  int push_warps;                  // pusher warps that take jobs (1..kPusherWarps)
+  int push_flags;                  // bit 0: plain (non-release) counter increment after the drain
+  const long long* epoch;          // a device word that grows with every invocation (barrier epoch), or null
+  int* progress;                   // highest pair tile (tagged with the epoch) this rank's GEMM has started
+  int push_lead;                   // raster groups the pushers may run ahead of the GEMM (0 = unlimited)
   // bounded waits
   int* status;
   unsigned long long timeout_ns;
@@ -200,11 +205,11 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
   const int jobs_per_block = P.num_in * P.p * P.split;
   const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
-  const int worker = blockIdx.x * kPusherWarps + pusher;
-  const int workers = gridDim.x * kPusherWarps;
+  const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
+  const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
   uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
   uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
-  for (long long job = worker; job < num_jobs && !w.dead; job += workers) {
+  auto do_job = [&](long long job) {
     const int mi = static_cast<int>(job / jobs_per_block);
     int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
     const int q = rest % P.split;
@@ -212,6 +217,27 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
     const int d = (rest % P.p + P.rank) % P.p;
     const int t = rest / P.p;
     const int row0 = mi * kTileM + q * sub_rows;
+    if (paced) {
+      // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
+      // the same schedule, so the peers consume at about this rank's pace; pushing faster only
+      // saturates the NVLink egress queue, behind which the GEMM's own loads then wait.
+      const int need = ((mi >> 1) / P.group_m - P.push_lead) * P.group_m;  // pair tile that must have started
+      if (need > 0 && lane == 0) {
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t it = 0;
+        while (ld_relaxed_sys_s32(P.progress) - base < need) {
+          nanosleep(200);
+          if ((++it & 0xff) == 0) {
+            if (should_abort(w)) break;
+            if (globaltimer_ns() - t0 > w.timeout_ns) {
+              report(w, kErrCounterTimeout, 41, mi);
+              break;
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
     const char* src = static_cast<const char*>(P.src[t]) +
                       (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
     char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
@@ -268,10 +294,29 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
       // whoever acquires the counter.
       bulk_wait_all();
       fence_proxy_async_all();
-      if (!w.dead) red_release_sys_add(reinterpret_cast<int*>(P.peer_counters[d]) + mi, 1);
+      if (!w.dead) {
+        int* ctr = reinterpret_cast<int*>(P.peer_counters[d]) + mi;
+        if (P.push_flags & 1)
+          red_relaxed_sys_add(ctr, 1);
+        else
+          red_release_sys_add(ctr, 1);
+      }
     }
     w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
-  }
+  };
+  // Two phases (as in fused_gemm_a2a_kernels.py:358-380): every pusher warp works on the first two
+  // raster groups, which the GEMM cannot start without; afterwards only `push_warps` warps per CTA
+  // continue, enough to stay ahead of the GEMM without saturating the NVLink egress queue that
+  // the GEMM's own loads share.
+  const long long first_jobs =
+      min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
+  for (long long job = blockIdx.x * kPusherWarps + pusher; job < first_jobs && !w.dead;
+       job += static_cast<long long>(gridDim.x) * kPusherWarps)
+    do_job(job);
+  if (pusher < P.push_warps)
+    for (long long job = first_jobs + blockIdx.x * P.push_warps + pusher; job < num_jobs && !w.dead;
+         job += static_cast<long long>(gridDim.x) * P.push_warps)
+      do_job(job);
   if (lane == 0) bulk_wait_all();
 }
 
@@ -435,6 +480,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
           const int blk = m * 2 + static_cast<int>(cta_rank);
           if (!counter_wait(P.counters + blk, P.target, w, 10, blk)) break;
           fence_proxy_async_global();
+          if (P.progress != nullptr && P.epoch != nullptr)
+            atomicMax(P.progress, (static_cast<int>(*P.epoch & 0x3fff) << 17) + m);
         }
         for (int kt = 0; kt < P.k_tiles; ++kt) {
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, w, 11)) break;

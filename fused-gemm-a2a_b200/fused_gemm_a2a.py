@@ -111,6 +111,7 @@ class _Comm:
         _native.lib()  # fail here, loudly, if the CUDA library was never built
         self.device = torch.device('cuda', torch.cuda.current_device())
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.progress = torch.zeros(1, dtype=torch.int32, device=self.device)  # GEMM progress for pusher pacing
         self.compiled = {}   # launch plans by geometry (nothing is compiled; kept for introspection)
         self.pool = {}
         self.projection_buffers = {}
@@ -247,7 +248,8 @@ class _Comm:
             _native.check(lib.fga_gemm_recv(
                 a.data_ptr(), a.shape[0], a.shape[1], b.data_ptr(), int(b_is_kn), output_width,
                 c.data_ptr(), aux[0].data_ptr(), aux[1].data_ptr(), counters.data_ptr(), sources,
-                num_in, src_rows, split, self.rank, self.p, roles, self.status.data_ptr(),
+                num_in, src_rows, split, self.rank, self.p, roles,
+                self.flags.data_ptr() + 8 * self.rank, self.progress.data_ptr(), self.status.data_ptr(),
                 _k.DEVICE_TIMEOUT_NS, stream))
 
     def recv_gemm(self, a, b, b_is_kn, c, peer_recv, peer_counters, counters, num_in, srcs,

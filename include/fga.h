@@ -89,12 +89,17 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
  * in [head][q|k|v|g][128] column order, rows >= src_rows as zeros, and bump peer d's counter of
  * that 128-row block; the GEMM c[recv_rows, n] = recv[recv_rows, k] * b^T consumes a row block
  * once its counter reaches p * num_in * split. roles: bit 0 GEMM, bit 1 pushers (both = 3).
+ * epoch / progress (both may be NULL): pacing of the pushers. epoch points at a device word that
+ * grows between invocations (the barrier flag of this rank); progress is a caller-owned device
+ * int32 in which the GEMM publishes the row tile it has reached, tagged with the epoch so that it
+ * never needs clearing; the pushers then stay a bounded number of raster groups ahead of it.
  * Reference: mode 'recv' with _push_jobs / _push_one
  * (fused_gemm_a2a_kernels.py:291-380, 764-772, 798-804). */
 int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_is_kn, int n,
                   void* c, const int64_t* peer_recv, const int64_t* peer_counters,
                   int32_t* counters, const void* const* srcs, int num_in, int src_rows, int split,
-                  int rank, int p, int roles, int32_t* status, uint64_t timeout_ns, void* stream);
+                  int rank, int p, int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
+                  uint64_t timeout_ns, void* stream);
 
 /* local: c[m, n] (=|+=) a * b^T with a as [m, k] (a_is_km == 0) or [k, m] (a_is_km != 0, read
  * transposed) and b as [n, k] or [k, n]. out_f32 selects FP32 output; accumulate (FP32 only) adds

@@ -112,7 +112,7 @@ def test_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in):
                                       outs[r].data_ptr(), t_recv.data_ptr(), t_cnt.data_ptr(),
                                       counters[r].data_ptr(),
                                       nat.ptr_array([t.data_ptr() for t in dev_inputs[r]]), num_in, tokens, split,
-                                      r, p, roles, status.data_ptr(), TIMEOUT_NS,
+                                      r, p, roles, None, None, status.data_ptr(), TIMEOUT_NS,
                                       torch.cuda.current_stream().cuda_stream)
             assert rc == 0, native.fga_last_error()
         torch.cuda.synchronize()
