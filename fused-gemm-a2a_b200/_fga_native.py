@@ -46,6 +46,10 @@ def _declare(l):
     l.fga_gemm_recv.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, vp, vp, vp,
                                 c_uint64, vp]
     l.fga_gemm_local.argtypes = [vp, i, vp, i, i, i, i, i64, i64, vp, i64, i, i, vp, c_uint64, vp]
+    l.fga_gemm_local_mx.argtypes = [vp, vp, i64, vp, vp, i64, i, i, i, vp, i64, i, i, vp, c_uint64, vp]
+    l.fga_gemm_push_mx.argtypes = [vp, vp, i64, i, i, vp, vp, i64, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
+    l.fga_gemm_recv_mx.argtypes = [vp, vp, vp, i, i, vp, vp, i64, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i,
+                                   vp, vp, vp, c_uint64, vp]
     l.fga_copy_rank_rows.argtypes = [pp, pp, i, i, i64, i64, i, vp, i, i, vp]
     l.fga_bias_grad_scratch_floats.argtypes = [i64, i]
     l.fga_bias_grad_scratch_floats.restype = i64
@@ -55,14 +59,16 @@ def _declare(l):
     l.fga_mx_quantize.argtypes = [vp, i64, i, i64, i64, vp, vp, i64, i, vp]
     for name in ('fga_symm_alloc', 'fga_symm_export', 'fga_symm_open', 'fga_symm_close',
                  'fga_symm_free', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
-                 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
+                 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
+                 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
                  'fga_mx_quantize'):
         getattr(l, name).restype = i
 
 
 EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 'fga_symm_alloc', 'fga_symm_export',
            'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_barrier', 'fga_gemm_push',
-           'fga_gemm_recv', 'fga_gemm_local', 'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
+           'fga_gemm_recv', 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
+           'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
            'fga_bias_grad', 'fga_bias_grad_static_capacity_floats', 'fga_bias_grad_static', 'fga_mx_quantize')
 
 

@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "aux_kernels.cuh"
+#include "mx_quant.cuh"
 
 namespace fga {
 
@@ -281,32 +282,6 @@ int launch_bias_grad_static(const void* dy, long long rows, int width, void* out
 // Scale bytes are stored in the tcgen05 128-row x 4-group swizzled layout
 // (fused_gemm_a2a_kernels.py:1195-1197). Padding rows/columns are written (payload 0, scale 127).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void mx_scale(float peak, int& exponent, float& inv_scale) {
-  exponent = 0;
-  if (peak > 0.f) {
-    const int bits = __float_as_int(peak);
-    exponent = (bits >> 23) - 135;
-    if ((bits & 0x7fffff) > 0x600000) exponent += 1;
-    exponent = max(-126, min(127, exponent));
-  }
-  inv_scale = __int_as_float((127 - exponent) << 23);
-  if (peak == __int_as_float(0x7f800000)) {
-    exponent = 128;
-    inv_scale = 0.f;
-  }
-}
-
-__device__ __forceinline__ long long mx_scale_offset(long long row, int group, int groups) {
-  return ((row / 128) * (groups / 4) + group / 4) * 512 + (row % 32) * 16 + (row % 128 / 32) * 4 +
-         group % 4;
-}
-
-__device__ __forceinline__ uint16_t to_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
 // Row-major source: one warp per (row, 256-column chunk); 4 lanes share a 32-group.
 __global__ void mx_quant_rows_kernel(const uint16_t* a, uint8_t* q, uint8_t* sf, long long rows,
                                      int k, long long rp, int kp, long long stride_row) {

@@ -18,16 +18,18 @@ static int env_int(const char* name, int fallback) {
 // CTA pairs that can be resident at once. A persistent grid never exceeds it: in recv mode the
 // resident CTAs wait for pusher jobs of every CTA of every rank, so a CTA that is not resident
 // would deadlock the group.
-static int resident_pairs(int threads, int* out) {
+static int resident_pairs(bool mx, int threads, int* out) {
   constexpr int kMaxDevices = 64;
-  static int cached[kMaxDevices][2];  // 0 = not queried yet; racing threads compute the same value
+  static int cached[kMaxDevices][2][3];  // 0 = not queried yet; racing threads compute the same value
   int dev = 0;
   FGA_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return set_error(kUnsupported, "device index %d out of range", dev);
-  const int slot = threads > 32 * kGemmWarps ? 1 : 0;
-  if (cached[dev][slot] == 0) {
-    FGA_CUDA(cudaFuncSetAttribute(ulysses_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kSmemBytes));
+  const int slot = threads <= 32 * kGemmWarps ? 0 : (threads <= 32 * (kGemmWarps + kPusherWarps) ? 1 : 2);
+  int& entry = cached[dev][mx ? 1 : 0][slot];
+  if (entry == 0) {
+    const void* fn = mx ? reinterpret_cast<const void*>(ulysses_gemm_kernel<true>)
+                        : reinterpret_cast<const void*>(ulysses_gemm_kernel<false>);
+    FGA_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * (sm_count() / 2));
     cfg.blockDim = dim3(threads);
@@ -40,11 +42,11 @@ static int resident_pairs(int threads, int* out) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    FGA_CUDA(cudaOccupancyMaxActiveClusters(&clusters, ulysses_gemm_kernel, &cfg));
+    FGA_CUDA(cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg));
     if (clusters < 1) return set_error(kCudaError, "no CTA pair of the GEMM kernel fits on this device");
-    cached[dev][slot] = clusters;
+    entry = clusters;
   }
-  *out = cached[dev][slot];
+  *out = entry;
   return kSuccess;
 }
 
@@ -64,18 +66,40 @@ static int encode_operand(CUtensorMap* map, const void* base, int mn_major, long
   return encode_tmap_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, rows, pitch, 64, 64);
 }
 
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cudaStream_t stream,
+                  const CUtensorMap* tsa = nullptr, const CUtensorMap* tsb = nullptr) {
+  const bool mx = tsa != nullptr;
   const int forced_stages = env_int("FGA_STAGES", 0);  // tuning knob: fewer pipeline stages
   if (forced_stages >= 2 && forced_stages <= P.stages) P.stages = forced_stages;
-  const int threads = 32 * (kGemmWarps + (P.mode == kRecv ? kPusherWarps : 0));
+  if (P.acc_stages == 0) P.acc_stages = 2;
+  const int threads =
+      32 * (kGemmWarps + (P.mode == kRecv ? kPusherWarps + (mx ? kQuantWarps : 0) : 0));
   int pairs = 0;
-  const int rc = resident_pairs(threads, &pairs);
+  const int rc = resident_pairs(mx, threads, &pairs);
   if (rc != kSuccess) return rc;
   const long long tiles = static_cast<long long>(P.m_tiles) * P.n_tiles;
   if (P.mode != kRecv && tiles < pairs) pairs = static_cast<int>(tiles);
-  ulysses_gemm_kernel<<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, P);
+  if (mx)
+    ulysses_gemm_kernel<true><<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, *tsa, *tsb, P);
+  else
+    ulysses_gemm_kernel<false><<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, ta, tb, P);
   FGA_LAUNCHED();
   return kSuccess;
+}
+
+// Block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 across the pair, N = bn.
+// The scale-byte selectors (bits 4-5 and 29-30) are filled in per K block by the kernel.
+static uint32_t make_idesc_mx(int bn) {
+  return (static_cast<uint32_t>(bn >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+// E4M3 operand [rows, kp] (K-major, 128-byte K steps) and its scale blocks [blocks, 512 B].
+static int encode_mx_operand(CUtensorMap* data, CUtensorMap* scales, const void* q, const void* sf,
+                             long long rows_padded, long long kp, int box_rows) {
+  int rc = encode_tmap_2d(data, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows_padded, kp, kp, box_rows, 128);
+  if (rc != kSuccess) return rc;
+  const long long blocks = (rows_padded / 128) * (kp / 128);
+  return encode_tmap_2d(scales, sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, blocks, 128, 128, 1, 128, false);
 }
 
 }  // namespace fga
@@ -247,6 +271,182 @@ int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m
   rc = encode_operand(&tb, b, P.b_mn, n, k, ldb, P.bn / 2);
   if (rc != kSuccess) return rc;
   return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+// ---- MXFP8 variants: operands are E4M3 [rows_padded, kp] with E8M0 scales in the tcgen05 layout,
+// exactly what fga_mx_quantize writes (rows padded to 256, kp to 128).
+
+int fga_gemm_local_mx(const void* aq, const void* sfa, int64_t a_rows_padded, const void* bq,
+                      const void* sfb, int64_t b_rows_padded, int m, int n, int kp, void* c, int64_t ldc,
+                      int out_f32, int accumulate, int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(aq && sfa && bq && sfb && c && status, "fga_gemm_local_mx: null argument");
+  FGA_REQUIRE(m >= 1 && n >= 128 && n % 128 == 0 && kp >= 128 && kp % 128 == 0,
+              "fga_gemm_local_mx: n and the padded K must be positive multiples of 128");
+  FGA_REQUIRE(a_rows_padded >= m && a_rows_padded % 256 == 0 && b_rows_padded >= n && b_rows_padded % 128 == 0,
+              "fga_gemm_local_mx: operand rows must be padded as the quantizer pads them");
+  FGA_REQUIRE(!accumulate || out_f32, "MXFP8 gradient accumulation requires FP32 output");
+  FGA_REQUIRE(ldc >= n && (ldc * (out_f32 ? 4 : 2)) % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0,
+              "fga_gemm_local_mx: output needs 16-byte aligned rows");
+  GemmParams P{};
+  P.mode = kLocal;
+  P.epi = out_f32 ? (accumulate ? kEpiF32Add : kEpiF32Store) : kEpiBf16;
+  P.bn = (n % 256 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.acc_stages = P.bn == 256 ? 1 : 2;
+  P.m_tiles = (m + 255) / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = kp / 128;
+  P.group_m = env_int("FGA_GROUP_M_LOCAL", 8);
+  P.stages = kMaxStages;
+  P.idesc = make_idesc_mx(P.bn);
+  P.p = 1;
+  P.c = c;
+  P.c_pitch = ldc;
+  P.c_rows = m;
+  P.segments = 1;
+  P.heads_per_rank = 1;
+  P.roles = 1;
+  P.sfa_kblocks = P.sfb_kblocks = kp / 128;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = encode_mx_operand(&ta, &tsa, aq, sfa, a_rows_padded, kp, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, kp, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
+}
+
+int fga_gemm_push_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int kp, int a_rows,
+                     const void* bq, const void* sfb, int64_t b_rows_padded, const void* bias, int segments,
+                     int n_segment, const int64_t* const* peer_heads, int64_t head_rows, int rank, int p,
+                     int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(aq && sfa && bq && sfb && peer_heads && status, "fga_gemm_push_mx: null argument");
+  FGA_REQUIRE(segments == 1 || segments == 3 || segments == 4,
+              "Expected one output projection or three/four QKV projections");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_push_mx: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(kp >= 128 && kp % 128 == 0, "fga_gemm_push_mx: padded K must be a multiple of 128");
+  FGA_REQUIRE(a_rows % 256 == 0 && a_rows <= a_rows_padded && a_rows <= head_rows,
+              "a_rows must be a tile multiple within the quantized rows and the head-side rank block");
+  FGA_REQUIRE(n_segment > 0 && n_segment % (p * 128) == 0,
+              "Push segment width must be a multiple of CP * tile N");
+  const int n = segments * n_segment;
+  FGA_REQUIRE(b_rows_padded >= n && b_rows_padded % 128 == 0, "fga_gemm_push_mx: weight rows must be padded");
+  for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_mx: null peer table %d", s);
+  GemmParams P{};
+  P.mode = kPush;
+  P.epi = kEpiBf16;
+  P.bn = ((n / 128) % 2 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.acc_stages = P.bn == 256 ? 1 : 2;
+  P.m_tiles = a_rows / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = kp / 128;
+  P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
+  P.stages = kMaxStages;
+  P.idesc = make_idesc_mx(P.bn);
+  P.rank = rank;
+  P.p = p;
+  P.bias = static_cast<const uint16_t*>(bias);
+  for (int s = 0; s < 4; ++s)
+    P.peer_heads[s] = reinterpret_cast<const long long*>(peer_heads[s < segments ? s : 0]);
+  P.segments = segments;
+  P.heads_per_rank = n_segment / p / 128;
+  P.head_pitch = n_segment / p;
+  P.head_rows = head_rows;
+  P.n_rotate = (P.n_tiles % p == 0) ? rank * (P.n_tiles / p) : 0;
+  P.roles = 1;
+  P.sfa_kblocks = P.sfb_kblocks = kp / 128;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = encode_mx_operand(&ta, &tsa, aq, sfa, a_rows_padded, kp, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, kp, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
+}
+
+int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_rows, int k, const void* bq,
+                     const void* sfb, int64_t b_rows_padded, int b_kp, int n, void* c,
+                     const int64_t* peer_recv, const int64_t* peer_counters, int32_t* counters,
+                     const void* const* srcs, int num_in, int src_rows, int split, int rank, int p,
+                     int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
+                     uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(recv && mx_recv && mx_scale && bq && sfb && c && peer_recv && peer_counters && counters && srcs &&
+                  status,
+              "fga_gemm_recv_mx: null argument");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_recv_mx: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(num_in == 1 || num_in == 3 || num_in == 4,
+              "Expected one output projection or three/four QKV projections");
+  FGA_REQUIRE(recv_rows >= 256 && recv_rows % 256 == 0, "fga_gemm_recv_mx: receive rows must be a multiple of 256");
+  FGA_REQUIRE(src_rows >= 1 && src_rows <= recv_rows,
+              "Receive source rows must be positive and fit the receive buffer");
+  FGA_REQUIRE(k % (p * num_in * 128) == 0, "Receive K must split evenly over peers and input segments");
+  FGA_REQUIRE(b_kp >= k && b_kp % 128 == 0, "fga_gemm_recv_mx: the weight's padded K must cover K");
+  FGA_REQUIRE(n >= 128 && n % 128 == 0 && b_rows_padded >= n && b_rows_padded % 128 == 0,
+              "GEMM mode must be push/recv and tile N must divide output width");
+  FGA_REQUIRE(split >= 1 && 128 % split == 0, "FUSED_PUSH_SPLIT must divide 128");
+  FGA_REQUIRE((roles & 3) != 0 && (roles & ~3) == 0, "fga_gemm_recv_mx: roles is a mask of 1 (GEMM) and 2 (pushers)");
+  for (int t = 0; t < num_in; ++t)
+    FGA_REQUIRE(srcs[t] && reinterpret_cast<uintptr_t>(srcs[t]) % 16 == 0,
+                "fga_gemm_recv_mx: source %d must be a 16-byte aligned device pointer", t);
+  GemmParams P{};
+  P.mode = kRecv;
+  P.epi = kEpiBf16;
+  P.bn = (n % 256 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.acc_stages = P.bn == 256 ? 1 : 2;
+  P.m_tiles = recv_rows / 256;
+  P.n_tiles = n / P.bn;
+  P.k_tiles = k / 128;
+  P.group_m = env_int("FGA_GROUP_M_RECV", 4);
+  P.stages = kMaxStages - 1;
+  {
+    const int hpr = k / (p * num_in * 128), sub_rows = 128 / split;
+    int units = hpr;
+    while (units > kPushBufBytes / 256 || hpr % units) --units;
+    int rows = 1;
+    if (units == hpr)
+      while (rows * 2 * units * 256 <= kPushBufBytes && rows * 2 <= sub_rows) rows *= 2;
+    P.push_units = units;
+    P.push_rows = rows;
+  }
+  P.idesc = make_idesc_mx(P.bn);
+  P.rank = rank;
+  P.p = p;
+  P.c = c;
+  P.c_pitch = n;
+  P.c_rows = recv_rows;
+  P.segments = 1;
+  P.heads_per_rank = k / (p * num_in * 128);
+  P.counters = counters;
+  P.quant_arrivals = p * num_in * split;
+  P.target = P.quant_arrivals + 16;
+  P.peer_recv = reinterpret_cast<const long long*>(peer_recv);
+  P.peer_counters = reinterpret_cast<const long long*>(peer_counters);
+  for (int t = 0; t < 4; ++t) P.src[t] = srcs[t < num_in ? t : 0];
+  P.num_in = num_in;
+  P.src_rows = src_rows;
+  P.split = split;
+  P.recv_k = k;
+  P.roles = roles;
+  P.push_warps = env_int("FGA_PUSHER_WARPS", 2);
+  if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
+  P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
+  P.epoch = reinterpret_cast<const long long*>(epoch);
+  P.progress = progress;
+  P.push_lead = env_int("FGA_PUSH_LEAD", 0);
+  P.quant_src = static_cast<const uint16_t*>(recv);
+  P.quant_q = static_cast<uint8_t*>(mx_recv);
+  P.quant_sf = static_cast<uint8_t*>(mx_scale);
+  P.sfa_kblocks = k / 128;
+  P.sfb_kblocks = b_kp / 128;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = encode_mx_operand(&ta, &tsa, mx_recv, mx_scale, recv_rows, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, b_kp, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
 }
 
 }  // extern "C"

@@ -23,6 +23,7 @@
 #pragma once
 #include "ptx.cuh"
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace fga {
 
@@ -36,10 +37,13 @@ constexpr int kPieceBytes = 128;        // epilogue row piece: 64 BF16 or 32 FP3
 constexpr int kSlotPitch = kPieceBytes + 16;  // 16-byte skew: conflict-free 16-byte stores
 constexpr int kStagingBytes = 128 * kSlotPitch;
 constexpr int kBarrierBytes = 256;
+constexpr int kSfStageBytes = 1536;     // MXFP8: 512 B of A scales + 2 x 512 B of B scales per stage
+constexpr int kQuantWarps = 2;          // MXFP8 recv: warps that quantize arrived BF16 row blocks
 constexpr int kGemmWarps = 6;           // TMA, MMA, 4 epilogue
 constexpr int kPusherWarps = 4;
 constexpr int kPushBufBytes = 4096;     // per pusher warp: two of these
-constexpr int kSmemBytes = kMaxStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+constexpr int kSmemBytes =
+    kMaxStages * (kStageBytes + kSfStageBytes) + kStagingBytes + kBarrierBytes + 1024;
 static_assert(kPusherWarps * 2 * kPushBufBytes == kStageBytes, "pusher buffers reuse one stage");
 
 enum GemmMode : int { kLocal = 0, kPush = 1, kRecv = 2 };
@@ -83,6 +87,13 @@ struct GemmParams {
   const long long* epoch;          // a device word that grows with every invocation (barrier epoch), or null
   int* progress;                   // highest pair tile (tagged with the epoch) this rank's GEMM has started
   int push_lead;                   // raster groups the pushers may run ahead of the GEMM (0 = unlimited)
+  // MXFP8 (E4M3 operands, one E8M0 scale per 32 K elements, K step = 128 elements)
+  int acc_stages;                  // TMEM accumulator stages: 2, or 1 when MXFP8 uses BN = 256
+  int sfa_kblocks, sfb_kblocks;    // 128-element K blocks per 128-row block in the A / B scale layouts
+  const uint16_t* quant_src;       // recv: this rank's BF16 receive buffer (source of the quantizer warps)
+  uint8_t* quant_q;                // recv: local E4M3 copy of the receive buffer (the GEMM's A operand)
+  uint8_t* quant_sf;               // recv: its E8M0 scales in the tcgen05 layout
+  int quant_arrivals;              // recv: counter value at which a row block is complete in BF16
   // bounded waits
   int* status;
   unsigned long long timeout_ns;
@@ -321,6 +332,49 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
 }
 
 // ---------------------------------------------------------------------------------------------
+// Receive-side quantizer warps (MXFP8 recv mode; the reference's _mx_quantize_received,
+// fused_gemm_a2a_kernels.py:1295-1343). Only BF16 crosses the links. Job = 8 rows of a 128-row
+// block: wait until the block's counter shows every BF16 arrival, quantize the rows along K into
+// the local E4M3 copy and its scale bytes, then add one completion to the same counter; the TMA
+// producer waits for arrivals + 16 completions before it loads the block.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void run_quantizers(const GemmParams& P, int worker_in_cta, int lane, WaitCtx& w) {
+  const long long k = P.recv_k;
+  const int groups = static_cast<int>(k >> 5);
+  const long long jobs = static_cast<long long>(P.m_tiles) * 2 * 16;
+  for (long long job = blockIdx.x * kQuantWarps + worker_in_cta; job < jobs && !w.dead;
+       job += static_cast<long long>(gridDim.x) * kQuantWarps) {
+    const int blk = static_cast<int>(job >> 4);
+    bool ok = true;
+    if (lane == 0) ok = counter_wait(P.counters + blk, P.quant_arrivals, w, 50, blk);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    __syncwarp();  // lane 0's acquire orders the other lanes' loads of the block behind it
+    if (!ok) {
+      w.dead = true;
+      break;
+    }
+    for (int r = 0; r < 8; ++r) {
+      const long long row = job * 8 + r;
+      for (long long c0 = 0; c0 < k; c0 += 256) {
+        const long long col = c0 + lane * 8;
+        const bool active = col < k;  // K is a multiple of 32: whole 4-lane groups drop out together
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (active) x = __ldcg(reinterpret_cast<const uint4*>(P.quant_src + row * k + col));
+        int sf_byte;
+        const uint2 q = mx_quantize8(x, sf_byte);
+        if (active) {
+          *reinterpret_cast<uint2*>(P.quant_q + row * k + col) = q;
+          if ((lane & 3) == 0)
+            P.quant_sf[mx_scale_offset(row, static_cast<int>(col >> 5), groups)] = static_cast<uint8_t>(sf_byte);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) red_release_sys_add(P.counters + blk, 1);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Epilogue for one 128-row x BN accumulator of this CTA. Thread = output row; the row leaves in
 // 128-byte pieces (64 BF16 or 32 FP32 columns), each staged in the thread's own shared slot and
 // shipped with one bulk copy, so no thread ever waits for another.
@@ -408,15 +462,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem
 // ---------------------------------------------------------------------------------------------
 // The kernel. blockDim = 192 (local, push) or 320 (recv: + 4 pusher warps). Grid = 2 * pairs.
 // ---------------------------------------------------------------------------------------------
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + kPusherWarps), 1)
+template <bool kMx>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + kPusherWarps + kQuantWarps), 1)
     ulysses_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_sfa,
+                        const __grid_constant__ CUtensorMap tmap_sfb,
                         const __grid_constant__ GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t push_bufs = smem_base + (kMaxStages - 1) * kStageBytes;  // recv mode: sixth stage
   const uint32_t staging = smem_base + kMaxStages * kStageBytes;
-  const uint32_t bars = staging + kStagingBytes;
+  const uint32_t sf0 = staging + kStagingBytes;  // MXFP8 scale stages
+  const uint32_t bars = sf0 + kMaxStages * kSfStageBytes;
   // barrier layout (8 bytes each): full[6], empty[6], tfull[2], tempty[2], pusher[4][2]
   const uint32_t full0 = bars, empty0 = bars + 8 * kMaxStages, tfull0 = bars + 16 * kMaxStages,
                  tempty0 = tfull0 + 16, push_bar0 = tempty0 + 16,
@@ -466,7 +524,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0 && gemm_on) {
-      const uint32_t tx_bytes = 2u * (kABytes + (P.bn >> 1) * 128u);
+      const uint32_t tx_bytes =
+          2u * (kABytes + (P.bn >> 1) * 128u + (kMx ? 512u + (P.bn >> 7) * 512u : 0u));
       const int b_half = P.bn >> 1;
       int s = 0;
       uint32_t ph = 0;
@@ -489,7 +548,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
           const uint32_t b_dst = a_dst + kABytes;
           const uint32_t full_leader = mapa(full0 + 8 * s, 0);
           if (leader) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
-          const int k0 = kt * kTileK;
+          const int k0 = kt * (kMx ? 128 : kTileK);
+          if constexpr (kMx) {
+            // Scale blocks of this K step: 512 B for this CTA's 128 rows of A, and one block per
+            // 128 columns of the whole N tile (both CTAs multiply their rows by every column).
+            const uint32_t sf_dst = sf0 + s * kSfStageBytes;
+            tma_load_2d_pair(sf_dst, &tmap_sfa, full_leader, 0, (a_row0 >> 7) * P.sfa_kblocks + kt);
+            const int nb0 = b_row0_of(P, n) >> 7;
+            for (int i = 0; i < (P.bn >> 7); ++i)
+              tma_load_2d_pair(sf_dst + 512 + i * 512, &tmap_sfb, full_leader, 0, (nb0 + i) * P.sfb_kblocks + kt);
+          }
           if (!P.a_mn) {
             tma_load_2d_pair(a_dst, &tmap_a, full_leader, k0, a_row0);
           } else {
@@ -532,10 +600,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
           const uint32_t b_addr = a_addr + kABytes;
           const uint64_t adesc = desc_hi | ((a_addr >> 4) & 0x3fffu) | (a_lbo << 16);
           const uint64_t bdesc = desc_hi | ((b_addr >> 4) & 0x3fffu) | (b_lbo << 16);
+          if constexpr (kMx) {
+            // Scales: shared -> TMEM (lane = row % 32, column = row / 32, byte = K group), then four
+            // K = 32 MMAs whose descriptors select byte 0..3 of those columns.
+            const uint32_t sf_addr = sf0 + s * kSfStageBytes;
+            const uint64_t sf_hi = (static_cast<uint64_t>(8u | (1u << 14))) << 32;  // SBO 128 B, no swizzle
+            const uint32_t sfa_t = tmem_base + 256, sfb_t = tmem_base + 260;
+            tc_cp_sf_pair(sfa_t, sf_hi | ((sf_addr >> 4) & 0x3fffu) | (1u << 16));
+            for (int i = 0; i < (P.bn >> 7); ++i)
+              tc_cp_sf_pair(sfb_t + 4 * i, sf_hi | (((sf_addr + 512 + i * 512) >> 4) & 0x3fffu) | (1u << 16));
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, P.idesc,
-                          (kt | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              mma_mxf8_pair(d_tmem, adesc + k * 2, bdesc + k * 2,
+                            P.idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), sfa_t,
+                            sfb_t, (kt | k) != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, P.idesc,
+                            (kt | k) != 0 ? 1u : 0u);
+          }
           tc_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs when the MMAs retire
           if (++s == stages) {
             s = 0;
@@ -544,7 +628,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
         }
         if (w.dead) break;
         tc_commit_pair(tfull0 + 8 * as, 3);  // accumulator ready in both CTAs
-        if (++as == 2) {
+        if (++as == P.acc_stages) {
           as = 0;
           aph ^= 1;
         }
@@ -572,7 +656,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
         const int row = m * 256 + static_cast<int>(cta_rank) * kTileM + row_in_cta;
         epilogue_tile(P, tmem_base + as * P.bn, quarter, lane, slot, row, b_row0_of(P, n),
                       mapa(tempty0 + 8 * as, 0), stores_pending);
-        if (++as == 2) {
+        if (++as == P.acc_stages) {
           as = 0;
           aph ^= 1;
         }
@@ -582,11 +666,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       bulk_wait_all();
       if (P.mode == kPush) fence_acq_rel_sys();
     }
-  } else {
+  } else if (warp < kGemmWarps + kPusherWarps) {
     // ------------------------------------------------------------------ pusher warps (recv mode)
     if (P.mode == kRecv && (P.roles & 2) != 0) {
       const int pusher = warp - kGemmWarps;
       run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, w);
+    }
+  } else {
+    // ------------------------------------------------------------------ quantizer warps (MXFP8 recv)
+    if constexpr (kMx) {
+      if (P.mode == kRecv && gemm_on) run_quantizers(P, warp - kGemmWarps - kPusherWarps, lane, w);
     }
   }
 

@@ -438,9 +438,22 @@ class _ProjectionWorkspace:
             self.mx_scale = buffers.mx_scale[:capacity * self.recv.shape[1] // 32]
 
     def run_push(self, a, weight, b_is_kn, segments, bias=None):
-        if self.precision == 'mxfp8':
-            raise NotImplementedError('The block-scaled MXFP8 GEMM is not part of this build yet')
         width = weight.shape[1] if b_is_kn else weight.shape[0]
+        if self.precision == 'mxfp8':
+            # Both operands are requantized from BF16 on every call, each along this GEMM's
+            # reduction axis (reference fused_gemm_a2a.py:439-448).
+            aq, sa = mxfp8_quantize(a)
+            wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+            comm = self.comm
+            validate_tile_n('push', MMA_N_OUT_PUSH if segments == 1 else MMA_N, width, comm.p,
+                            width // segments, segments, self.head_dim)
+            tables = _native.ptr_array([t.data_ptr() for t in self.peer_heads[:segments]])
+            _native.check(_native.lib().fga_gemm_push_mx(
+                aq.data_ptr(), sa.data_ptr(), aq.shape[0], aq.shape[1], self.capacity, wq.data_ptr(),
+                sb.data_ptr(), wq.shape[0], 0 if bias is None else bias.data_ptr(), segments,
+                width // segments, tables, self.capacity, comm.rank, comm.p, comm.status.data_ptr(),
+                _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+            return
         self.comm.gemm('push', a, weight, b_is_kn, self.heads[0], self.peer_heads, self.counters, 0,
                        width // segments, segments, a_rows=self.capacity, head_dim=self.head_dim,
                        bias=bias)
@@ -455,7 +468,21 @@ class _ProjectionWorkspace:
         if shape[0] % self.comm.p:
             raise ValueError('Head-side rows must divide evenly over CP ranks')
         if self.precision == 'mxfp8':
-            raise NotImplementedError('The block-scaled MXFP8 GEMM is not part of this build yet')
+            # Only BF16 crosses the links; quantizer warps inside the kernel convert each arrived
+            # row block into the local E4M3 copy that the GEMM reads (reference fused_gemm_a2a.py:465-470).
+            comm = self.comm
+            wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+            k = self.recv.shape[1]
+            split = comm.push_split(self.recv, len(inputs), comm.p)
+            sources = _native.ptr_array([t.data_ptr() for t in inputs])
+            _native.check(_native.lib().fga_gemm_recv_mx(
+                self.recv.data_ptr(), self.mx_recv.data_ptr(), self.mx_scale.data_ptr(), self.capacity, k,
+                wq.data_ptr(), sb.data_ptr(), wq.shape[0], wq.shape[1], out.shape[1], out.data_ptr(),
+                self.peer_recv.data_ptr(), self.peer_counters.data_ptr(), self.counters.data_ptr(), sources,
+                len(inputs), shape[0] // comm.p, split, comm.rank, comm.p, roles,
+                comm.flags.data_ptr() + 8 * comm.rank, comm.progress.data_ptr(), comm.status.data_ptr(),
+                _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+            return
         self.comm.gemm('recv', self.recv, weight, b_is_kn, out, [self.peer_recv, self.peer_counters],
                        self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
                        head_dim=self.head_dim, src_rows=shape[0] // self.comm.p, roles=roles)

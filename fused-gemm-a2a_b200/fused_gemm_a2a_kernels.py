@@ -210,9 +210,39 @@ def bf16_wgrad(dy, x, out, status, *, accumulate=False):
     return out
 
 
+_local_status = {}
+
+
+def _status_word(device):
+    """A per-device status word for kernels launched outside a CP group (bounded-wait reports)."""
+    word = _local_status.get(device)
+    if word is None:
+        word = _local_status[device] = torch.zeros(4, dtype=torch.int32, device=device)
+    return word
+
+
+def mxfp8_gemm(a, sa, b, sb, out, m, n, status, *, accumulate=False):
+    """out[m, n] (=|+=) dequant(a) @ dequant(b)^T for operands produced by mxfp8_quantize (same
+    padded K); block-scaled tcgen05 MMAs with FP32 accumulation."""
+    if a.shape[1] != b.shape[1]:
+        raise ValueError('MXFP8 operands must be quantized over the same padded K')
+    _native.check(_native.lib().fga_gemm_local_mx(
+        a.data_ptr(), sa.data_ptr(), a.shape[0], b.data_ptr(), sb.data_ptr(), b.shape[0], m, n, a.shape[1],
+        out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+        status.data_ptr(), DEVICE_TIMEOUT_NS, _stream()))
+    return out
+
+
 def mxfp8_wgrad(dy, x, out, *, accumulate=False):
-    """MXFP8 weight gradient (reference fused_gemm_a2a_kernels.py:1398-1421): both operands are
-    requantized along the token axis and multiplied by the block-scaled GEMM."""
+    """MXFP8 weight gradient out[N_out, K] (=|+=) dy[T, N_out]^T x[T, K]: both operands are
+    requantized from BF16 along the token axis (the new reduction axis; FP8 payloads are never
+    transposed) and multiplied by the block-scaled GEMM; FP32 outputs may accumulate in place
+    (reference fused_gemm_a2a_kernels.py:1398-1421)."""
     if accumulate and out.dtype != torch.float32:
         raise ValueError('MXFP8 gradient accumulation requires FP32 output')
-    raise NotImplementedError('The block-scaled MXFP8 GEMM is not part of this build yet')
+    if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous():
+        raise ValueError('MXFP8 weight gradient needs a contiguous BF16 or FP32 output')
+    dq, ds = mxfp8_quantize(dy.T)
+    xq, xs = mxfp8_quantize(x.T)
+    return mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1], _status_word(out.device),
+                      accumulate=accumulate)

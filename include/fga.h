@@ -111,6 +111,35 @@ int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m
                    int64_t lda, int64_t ldb, void* c, int64_t ldc, int out_f32, int accumulate,
                    int32_t* status, uint64_t timeout_ns, void* stream);
 
+/* ---- MXFP8 variants -----------------------------------------------------------------------
+ * Same three modes with E4M3 operands and one E8M0 scale per 32 elements of the reduction axis,
+ * block-scaled tcgen05 MMAs, FP32 accumulation. Operands are what fga_mx_quantize writes: payload
+ * [rows_padded, kp] (rows padded to 256, kp to a multiple of 128) and scale bytes in the tcgen05
+ * 128-row x 4-group layout. Only BF16 ever crosses the links.
+ * Reference: UlyssesGemm with mxfp8 (fused_gemm_a2a_kernels.py:445-502, 557-579, 834-866),
+ * mxfp8_wgrad (1398-1421) and the receive-side quantizer _mx_quantize_received (1295-1343). */
+
+/* c[m, n] (=|+=) dequant(aq) * dequant(bq)^T over kp. */
+int fga_gemm_local_mx(const void* aq, const void* sfa, int64_t a_rows_padded, const void* bq,
+                      const void* sfb, int64_t b_rows_padded, int m, int n, int kp, void* c, int64_t ldc,
+                      int out_f32, int accumulate, int32_t* status, uint64_t timeout_ns, void* stream);
+
+/* push with quantized activations aq [a_rows_padded, kp] and weights bq [b_rows_padded, kp]. */
+int fga_gemm_push_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int kp, int a_rows,
+                     const void* bq, const void* sfb, int64_t b_rows_padded, const void* bias, int segments,
+                     int n_segment, const int64_t* const* peer_heads, int64_t head_rows, int rank, int p,
+                     int32_t* status, uint64_t timeout_ns, void* stream);
+
+/* recv: the pushers move BF16 into the peers' receive buffers as in fga_gemm_recv; two more warps
+ * per CTA quantize every arrived 128-row block of `recv` into mx_recv [recv_rows, k] / mx_scale
+ * (8 rows per job, 16 completions per block on the same counter) and the GEMM reads those. */
+int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_rows, int k, const void* bq,
+                     const void* sfb, int64_t b_rows_padded, int b_kp, int n, void* c,
+                     const int64_t* peer_recv, const int64_t* peer_counters, int32_t* counters,
+                     const void* const* srcs, int num_in, int src_rows, int split, int rank, int p,
+                     int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
+                     uint64_t timeout_ns, void* stream);
+
 /* ---- auxiliary kernels -------------------------------------------------------------------- */
 
 /* Replaces resize_rank_rows (fused_gemm_a2a_kernels.py:1145-1188). in/out: `segments` BF16
