@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument('--heads', type=int, default=32)
     ap.add_argument('--gate', action='store_true')
     ap.add_argument('--bias', action='store_true')
+    ap.add_argument('--precision', default='bf16', choices=('bf16', 'mxfp8'))
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer measurement')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-graphs', action='store_true', help='launch eagerly instead of replaying CUDA graphs')
@@ -324,7 +325,7 @@ def run_gpu_arm(args):
         import fused_gemm_a2a as fused
         lib = _fga_native.lib()
         launches = lib.fga_launch_count
-        ws = fused.FusedGemmA2AWorkspace(hidden, heads, m, gate=args.gate)
+        ws = fused.FusedGemmA2AWorkspace(hidden, heads, m, gate=args.gate, precision=args.precision)
         wq = interleave(w_seg, heads, d).contiguous().requires_grad_()
         wo_p = wo.clone().requires_grad_()
         bq_p = interleave(bq, heads, d).contiguous().requires_grad_() if args.bias else None
@@ -453,7 +454,7 @@ def run_gpu_arm(args):
 
     # ---- the GEMM kernel alone: CUDA events around every launch of it during extra steps
     roofline = None
-    if args.impl == 'fused':
+    if args.impl == 'fused' and args.precision == 'bf16':
         peak, peak_source = measured_peaks()
         records, others = [], []
 
@@ -567,7 +568,8 @@ def run_gpu_arm(args):
     line = dict(
         metric=METRIC, value=world * per_gpu_tflops, unit=UNIT, n_gpus=world, steps=args.steps,
         warmup=max(args.warmup, 3), ms_per_step=ms_per_step, higher_is_better=True, scaling='strong',
-        vs_baseline=None, dtype='bf16', data='synthetic', impl=args.impl,
+        vs_baseline=None, dtype='bf16' if args.precision == 'bf16' else 'mxfp8 (e4m3 payload, e8m0 scale per 32, fp32 accumulate)',
+        data='synthetic', impl=args.impl,
         config=dict(workload=f'{args.tokens} total tokens, H={hidden}, {heads}x{d} heads, CP={world} '
                              f'(M={m} per rank), QKV{"G" if args.gate else ""} + output projection, forward + dgrad + wgrad'
                              f'{", bias" if args.bias else ", no bias"}',

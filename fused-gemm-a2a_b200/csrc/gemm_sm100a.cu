@@ -218,7 +218,10 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   P.split = split;
   P.recv_k = k;
   P.roles = roles;
-  P.push_warps = env_int("FGA_PUSHER_WARPS", 2);  // warps per CTA that keep pushing after the first groups
+  // Warps per CTA that keep pushing after the first groups: all of them while at least half of the
+  // traffic stays on this GPU, two once most of it crosses NVLink (more only congest the egress
+  // queue that the GEMM's own loads share).
+  P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
   P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
   P.epoch = reinterpret_cast<const long long*>(epoch);
@@ -428,7 +431,10 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   P.split = split;
   P.recv_k = k;
   P.roles = roles;
-  P.push_warps = env_int("FGA_PUSHER_WARPS", 2);
+  // Warps per CTA that keep pushing after the first groups: all of them while at least half of the
+  // traffic stays on this GPU, two once most of it crosses NVLink (more only congest the egress
+  // queue that the GEMM's own loads share).
+  P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
   P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
   P.epoch = reinterpret_cast<const long long*>(epoch);

@@ -96,6 +96,54 @@ def main():
         if rank == 0:
             print(f'PASS gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm}', flush=True)
 
+    # MXFP8: only BF16 crosses the links; expected values quantize every GEMM's operands along its
+    # reduction axis on the CPU (E4M3 + E8M0/32) and multiply the exact dequantized values
+    import numpy as np
+    from oracle import mxfp8_oracle as mx
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def mm(a, b):
+        return torch.from_numpy(mx.mx_matmul(bits(a), bits(b))).to(BF)
+
+    g = torch.Generator().manual_seed(99)
+    wq = (torch.randn(3 * hidden, hidden, generator=g) / 32).to(BF)
+    wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+    ws = FusedGemmA2AWorkspace(hidden, heads, 600, precision='mxfp8')
+    wq_d, wo_d = wq.to(dev).requires_grad_(), wo.to(dev).requires_grad_()
+    qkv = FusedQKVProjection(hidden, heads, weight=wq_d)
+    proj = FusedOutputProjection(hidden, heads, weight=wo_d)
+    hpr = heads // p
+    for tokens in (300, 129):
+        g = torch.Generator().manual_seed(555 * tokens + rank)
+        x = torch.randn(tokens, hidden, generator=g).to(BF).to(dev).requires_grad_()
+        grads = [torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev) for _ in range(3)]
+        o = torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev).requires_grad_()
+        dy = torch.randn(tokens, hidden, generator=g).to(BF).to(dev)
+        outs = qkv(x, ws)
+        dx, dwq = torch.autograd.grad(outs, [x, wq_d], grads)
+        y = proj(o, ws)
+        do, dwo = torch.autograd.grad(y, [o, wo_d], dy)
+        torch.cuda.synchronize()
+        ws.comm.check_status()
+        xs, dys, all_o = gather(x.detach()), gather(dy), gather(o.detach())
+        all_grads = list(zip(*[gather(t) for t in grads]))
+        plain = UlyssesOracle(p, hidden, heads, 3)
+        for seg in range(3):
+            want = torch.cat([mm(xr, wq).view(tokens, heads, 3, d)[:, rank * hpr:(rank + 1) * hpr, seg] for xr in xs])
+            close(outs[seg], want, f'mxfp8 segment {seg}')
+        dyq = plain.qkv_recv_buffer(all_grads, rank)
+        close(dx, mm(dyq, wq.t()), 'mxfp8 dx')
+        close(dwq, mm(dyq.t(), xs[rank].t()), 'mxfp8 dW_qkv')
+        o_seq = plain.out_recv_buffer(all_o, rank)
+        close(y, mm(o_seq, wo), 'mxfp8 y')
+        full_do = torch.cat([mm(dyr, wo.t())[:, rank * hpr * d:(rank + 1) * hpr * d] for dyr in dys])
+        close(do, full_do.view(p * tokens, hpr, d), 'mxfp8 dO')
+        close(dwo, mm(dys[rank].t(), o_seq.t()), 'mxfp8 dW_o')
+    if rank == 0:
+        print('PASS mxfp8', flush=True)
+
     # CUDA graph: one captured step replayed with changed inputs
     tokens, segments = 333, 3
     ws = FusedGemmA2AWorkspace(hidden, heads, 600)

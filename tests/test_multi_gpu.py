@@ -21,4 +21,5 @@ def test_fused_modules_across_gpus(native):
     sys.stdout.write(result.stdout[-4000:])
     sys.stderr.write(result.stderr[-4000:])
     assert result.returncode == 0
+    assert 'PASS mxfp8' in result.stdout
     assert 'PASS cuda graph replay' in result.stdout
