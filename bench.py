@@ -36,6 +36,11 @@ METRIC = 'fused QKV + output projection fwd+bwd throughput (131072 tokens, H=409
 UNIT = 'TFLOP/s'
 NOMINAL_BF16_TFLOPS = 2250.0
 LINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool (900 nominal)
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per FLOP of the GEMM kernel, from the ncu
+# captures of `--kernel-case gemm_nt` (670.4 MB) and `--kernel-case wgrad` (1296.8 MB), both
+# 824.6 GFLOP launches at 8192 tokens (profiles/ulysses_gemm_kernel_bf16_*.md). The benchmark's
+# launches are too large to capture; traffic grows with the rows, so it is scaled by the FLOPs.
+DRAM_BYTES_PER_FLOP = dict(gemm=670.4e6 / 824.6e9, wgrad=1296.8e6 / 824.6e9)
 
 
 def parse_args():
@@ -80,7 +85,7 @@ class ClockSampler:
     """nvidia-smi clock / throttle samples of one GPU while a region runs."""
     QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
-             'clocks_event_reasons.sw_power_cap')
+             'clocks_event_reasons.sw_power_cap,power.limit')
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
@@ -118,7 +123,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        clocks, max_clock, reasons, power = [], None, set(), []
+        clocks, max_clock, reasons, power, limit = [], None, set(), [], None
         names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
         window = self.lines[self.first:self.last] or self.lines[-3:]
         for line in window:
@@ -134,9 +139,14 @@ class ClockSampler:
             for name, flag in zip(names, parts[3:7]):
                 if flag.lower().startswith('active'):
                     reasons.add(name)
+            if len(parts) > 7:
+                try:
+                    limit = float(parts[7])
+                except ValueError:
+                    pass
         clocks.sort()
         return dict(sm_mhz=clocks[len(clocks) // 2] if clocks else None, sm_max_mhz=max_clock,
-                    power_w_max=max(power) if power else None, reasons=sorted(reasons),
+                    power_w_max=max(power) if power else None, power_limit_w=limit, reasons=sorted(reasons),
                     samples=len(clocks))
 
 
@@ -499,8 +509,18 @@ def run_gpu_arm(args):
         gemm_ms, = max_over_ranks([gemm_ms])
         achieved = gemm_flops_total / (gemm_ms * 1e-3) / 1e12
         a2a_bytes = 2.0 * m * (segments + 1) * hidden * 2 * (p - 1) / p  # both directions' payload per step
+        # operands and outputs of the six GEMMs of a step: activations and their gradients are touched
+        # by the forward, dgrad and wgrad launch; the weight is read twice and its BF16 gradient written
+        algorithmic_bytes = sum(2.0 * (3 * (m * hidden + m * s * hidden) + 3 * s * hidden * hidden)
+                                for s in (segments, 1))
+        traffic = sum(f * DRAM_BYTES_PER_FLOP['wgrad' if 'wgrad' in name else 'gemm']
+                      for name, _, _, f in records) / max(1, len(records))
         roofline = dict(bound='tensor', kernel='ulysses_gemm_kernel', achieved=achieved, peak=peak, unit='TFLOP/s',
-                        frac=achieved / peak, traffic=None, peak_source=peak_source,
+                        frac=achieved / peak, traffic=traffic,
+                        traffic_note='bytes per launch (mean over the 6 launches of a step), scaled by FLOPs from ncu '
+                                     'captures of 8192-token launches; algorithmic bytes per launch: '
+                                     f'{algorithmic_bytes / 6:.3e}',
+                        peak_source=peak_source,
                         launches_timed=len(records), avg_launch_ms=gemm_ms / max(1, len(records)),
                         gemm_share_of_step=gemm_ms / extra / ms_per_step,
                         frac_of_nominal_2250=achieved / NOMINAL_BF16_TFLOPS,

@@ -8,11 +8,22 @@
 
 namespace fga {
 
+// CTA pairs that only push in recv launches (see GemmParams::push_pairs); FGA_PUSH_PAIRS overrides.
+constexpr int kDefaultPushPairs = 0;
+
 static int env_int(const char* name, int fallback) {
   const char* v = getenv(name);
   if (v == nullptr || *v == '\0') return fallback;
   const int x = atoi(v);
   return x > 0 ? x : fallback;
+}
+
+// Like env_int, for knobs where 0 is a setting of its own.
+static int env_int0(const char* name, int fallback) {
+  const char* v = getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  const int x = atoi(v);
+  return x >= 0 ? x : fallback;
 }
 
 // CTA pairs that can be resident at once. A persistent grid never exceeds it: in recv mode the
@@ -72,19 +83,43 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cu
   const int forced_stages = env_int("FGA_STAGES", 0);  // tuning knob: fewer pipeline stages
   if (forced_stages >= 2 && forced_stages <= P.stages) P.stages = forced_stages;
   if (P.acc_stages == 0) P.acc_stages = 2;
+  if (P.k_splits < 1) P.k_splits = 1;
   const int threads =
       32 * (kGemmWarps + (P.mode == kRecv ? kPusherWarps + (mx ? kQuantWarps : 0) : 0));
   int pairs = 0;
   const int rc = resident_pairs(mx, threads, &pairs);
   if (rc != kSuccess) return rc;
-  const long long tiles = static_cast<long long>(P.m_tiles) * P.n_tiles;
-  if (P.mode != kRecv && tiles < pairs) pairs = static_cast<int>(tiles);
+  const long long units = static_cast<long long>(P.m_tiles) * P.n_tiles * P.k_splits;
+  if (P.mode != kRecv && units < pairs) pairs = static_cast<int>(units);
   if (mx)
     ulysses_gemm_kernel<true><<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, *tsa, *tsb, P);
   else
     ulysses_gemm_kernel<false><<<2 * pairs, threads, kSmemBytes, stream>>>(ta, tb, ta, tb, P);
   FGA_LAUNCHED();
   return kSuccess;
+}
+
+// Shares of the K steps per output tile for an FP32 gradient GEMM. A persistent grid of `pairs`
+// CTA pairs runs ceil(tiles / pairs) waves and the last one may be mostly empty (256 tiles on 74
+// pairs: 3.46 waves, 86 % efficiency). Cutting K multiplies the work units and fills the last wave;
+// every unit adds its partial tile with bulk reductions, so no second pass is needed. The smallest
+// split count that reaches 97 % wave efficiency is taken, each share keeping at least 32 K steps.
+static int choose_k_splits(long long tiles, int k_tiles, int pairs) {
+  const int forced = env_int("FGA_WGRAD_SPLITS", 0);
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 8; ++s) {
+    if (s > 1 && k_tiles / s < 32) break;
+    const long long units = tiles * s;
+    const double eff = static_cast<double>(units) / (static_cast<double>((units + pairs - 1) / pairs) * pairs);
+    if (s == forced) return s;
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (forced == 0 && eff >= 0.97) return s;
+  }
+  return best;
 }
 
 // Block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 across the pair, N = bn.
@@ -227,6 +262,7 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   P.epoch = reinterpret_cast<const long long*>(epoch);
   P.progress = progress;
   P.push_lead = env_int("FGA_PUSH_LEAD", 0);
+  P.push_pairs = env_int0("FGA_PUSH_PAIRS", kDefaultPushPairs);
   P.status = status;
   P.timeout_ns = timeout_ns;
   CUtensorMap ta, tb;
@@ -273,6 +309,18 @@ int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m
   if (rc != kSuccess) return rc;
   rc = encode_operand(&tb, b, P.b_mn, n, k, ldb, P.bn / 2);
   if (rc != kSuccess) return rc;
+  if (out_f32) {
+    int pairs = 0;
+    rc = resident_pairs(false, 32 * kGemmWarps, &pairs);
+    if (rc != kSuccess) return rc;
+    P.k_splits = choose_k_splits(static_cast<long long>(P.m_tiles) * P.n_tiles, P.k_tiles, pairs);
+    if (P.k_splits > 1 && !accumulate) {
+      // The shares add into the output, so a plain store becomes zero fill + accumulate.
+      FGA_CUDA(cudaMemset2DAsync(c, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(n) * 4,
+                                 static_cast<size_t>(m), static_cast<cudaStream_t>(stream)));
+      P.epi = kEpiF32Add;
+    }
+  }
   return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
 }
 
@@ -440,6 +488,7 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   P.epoch = reinterpret_cast<const long long*>(epoch);
   P.progress = progress;
   P.push_lead = env_int("FGA_PUSH_LEAD", 0);
+  P.push_pairs = env_int0("FGA_PUSH_PAIRS", kDefaultPushPairs);
   P.quant_src = static_cast<const uint16_t*>(recv);
   P.quant_q = static_cast<uint8_t*>(mx_recv);
   P.quant_sf = static_cast<uint8_t*>(mx_scale);

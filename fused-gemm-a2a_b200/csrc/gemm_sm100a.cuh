@@ -18,8 +18,10 @@
 // uses cluster multicast. Every wait is bounded: on expiry the waiter records an error in the
 // caller's status word, all roles drain, TMEM is freed and the kernel returns.
 //
-// Shared memory (215 KiB): local/push run 6 pipeline stages of 32 KiB; recv runs 5 stages and
+// Shared memory (220 KiB): local/push run 6 pipeline stages of 32 KiB; recv runs 5 stages and
 // gives the sixth to the pusher warps (4 warps x 2 buffers x 4 KiB); 18 KiB of epilogue staging.
+// A recv launch may set CTA pairs aside that only push (GemmParams::push_pairs): all ten warps of
+// such a CTA run the pusher loop with three-slot rings in the otherwise unused pipeline stages.
 #pragma once
 #include "ptx.cuh"
 #include "common.cuh"
@@ -42,9 +44,13 @@ constexpr int kQuantWarps = 2;          // MXFP8 recv: warps that quantize arriv
 constexpr int kGemmWarps = 6;           // TMA, MMA, 4 epilogue
 constexpr int kPusherWarps = 4;
 constexpr int kPushBufBytes = 4096;     // per pusher warp: two of these
+constexpr int kDedWarps = kGemmWarps + kPusherWarps;  // warps that push in a CTA that only pushes
+constexpr int kDedRing = 3;             // ring slots per warp there (the pipeline stages are free)
 constexpr int kSmemBytes =
     kMaxStages * (kStageBytes + kSfStageBytes) + kStagingBytes + kBarrierBytes + 1024;
 static_assert(kPusherWarps * 2 * kPushBufBytes == kStageBytes, "pusher buffers reuse one stage");
+static_assert(kDedWarps * kDedRing * (kPushBufBytes + 8) <= (kMaxStages - 1) * kStageBytes,
+              "rings of a pushing-only CTA fit below the sixth stage");
 
 enum GemmMode : int { kLocal = 0, kPush = 1, kRecv = 2 };
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Store = 1, kEpiF32Add = 2 };
@@ -55,6 +61,8 @@ struct GemmParams {
   int bn;                         // 128 or 256
   int stages;                     // pipeline stages in use (<= kMaxStages)
   int group_m;                    // pair tiles per raster group (N varies fastest inside a group)
+  int k_splits;                   // work units per output tile, each a contiguous share of the K steps
+                                  // (> 1 only with the FP32 reduce-add epilogue)
   int a_mn, b_mn;                 // 1 = operand is MN-major in global memory (transposed read)
   uint32_t idesc;                 // tcgen05 instruction descriptor
   int mode, epi;
@@ -87,6 +95,7 @@ struct GemmParams {
   const long long* epoch;          // a device word that grows with every invocation (barrier epoch), or null
   int* progress;                   // highest pair tile (tagged with the epoch) this rank's GEMM has started
   int push_lead;                   // raster groups the pushers may run ahead of the GEMM (0 = unlimited)
+  int push_pairs;                  // CTA pairs at the end of the grid that only push (0 = every CTA pushes)
   // MXFP8 (E4M3 operands, one E8M0 scale per 32 K elements, K step = 128 elements)
   int acc_stages;                  // TMEM accumulator stages: 2, or 1 when MXFP8 uses BN = 256
   int sfa_kblocks, sfb_kblocks;    // 128-element K blocks per 128-row block in the A / B scale layouts
@@ -186,6 +195,23 @@ __device__ __forceinline__ void tile_coords(const GemmParams& P, int t, int& m, 
   m = g * P.group_m + (r - n * gm);
 }
 
+// Work unit u of the grid's sequence -> (output tile, K-step range). With k_splits > 1 the split
+// index varies slowest, so a wave of CTA pairs works on one K range and the operands it shares
+// stay in L2; every unit adds its partial tile into the FP32 output with bulk reductions.
+__device__ __forceinline__ void unit_coords(const GemmParams& P, int u, int total_tiles, int& t, int& kt0,
+                                            int& kt1) {
+  if (P.k_splits <= 1) {
+    t = u;
+    kt0 = 0;
+    kt1 = P.k_tiles;
+    return;
+  }
+  const int s = u / total_tiles;
+  t = u - s * total_tiles;
+  kt0 = static_cast<int>(static_cast<long long>(s) * P.k_tiles / P.k_splits);
+  kt1 = static_cast<int>(static_cast<long long>(s + 1) * P.k_tiles / P.k_splits);
+}
+
 // First B row (weight row / output column) of N tile n. Push mode rotates the N order by rank.
 __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
   if (P.mode == kPush) {
@@ -201,12 +227,24 @@ __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
 // buffer, columns in Megatron order [head][q|k|v|g][D], rows past src_rows as zeros; then one
 // release-increment of d's counter for that row block (fused_gemm_a2a_kernels.py:291-380 is the
 // reference's register-copy version). Here one lane per warp drives the TMA unit: a chunk of up
-// to 4 KiB is bulk-loaded from local memory into one of the warp's two shared buffers and
+// to 4 KiB is bulk-loaded from local memory into a slot of the warp's ring of shared buffers and
 // bulk-stored to the peer in 256-byte head units (or whole rows when the columns are contiguous),
-// so the data never passes through registers and remote stores queue in the copy engine.
+// so the data never passes through registers and remote stores queue in the copy engine. The load
+// of the next chunk is started before the stores of the current one are issued.
+//
+// The warp takes jobs job_begin, job_begin + job_stride, ... < job_end. kRing = slots in its ring
+// (buf0 / bar0: kRing buffers of kPushBufBytes and kRing mbarriers).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane, uint32_t buf0,
-                                            uint32_t bar0, WaitCtx& w) {
+struct PushRing {
+  uint32_t seq = 0;     // chunks started on this ring (selects the slot)
+  uint32_t parity = 0;  // bit b: phase of slot b's next load completion (lane 0's copy is the one used)
+};
+
+template <int kRing>
+__device__ __noinline__ void run_pushers(const GemmParams& P, long long job_begin, long long job_end,
+                                         long long job_stride, int lane, uint32_t buf0, uint32_t bar0,
+                                         PushRing& ring, WaitCtx& w) {
+  static_assert(kRing >= 2 && kRing <= 8, "ring depth");
   const int hpr = P.heads_per_rank;
   const int row_bytes = hpr * 256;
   const int sub_rows = kTileM / P.split;
@@ -215,12 +253,10 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   const int chunk_row_bytes = upp * 256;
   const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
   const int jobs_per_block = P.num_in * P.p * P.split;
-  const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
   const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
   const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
-  uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
-  uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
-  auto do_job = [&](long long job) {
+  uint32_t seq = ring.seq, parity = ring.parity;
+  for (long long job = job_begin; job < job_end && !w.dead; job += job_stride) {
     const int mi = static_cast<int>(job / jobs_per_block);
     int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
     const int q = rest % P.split;
@@ -252,8 +288,8 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
     const char* src = static_cast<const char*>(P.src[t]) +
                       (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
     char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
-    for (int c = 0; c < chunks_per_job; ++c) {
-      int r0, u0;
+    // Chunk c of the job: rows [r0, r0 + rpc) x head units [u0, u0 + upp); `valid` rows exist in the source.
+    auto geometry = [&](int c, int& r0, int& u0, int& valid) {
       if (pieces_per_row == 1) {
         r0 = c * rpc;
         u0 = 0;
@@ -261,45 +297,63 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
         r0 = c / pieces_per_row;
         u0 = (c - r0 * pieces_per_row) * upp;
       }
-      const int b = issued & 1;
+      valid = max(0, min(rpc, P.src_rows - (row0 + r0)));
+    };
+    // Claim the chunk's ring slot and start its load; rows beyond the logical count become zeros.
+    auto start = [&](int c) {
+      int r0, u0, valid;
+      geometry(c, r0, u0, valid);
+      const int b = static_cast<int>((seq + c) % kRing);
       const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
-      const int valid = max(0, min(rpc, P.src_rows - (row0 + r0)));  // rows that exist in the source
-      if (lane == 0) bulk_wait_read<1>();  // the group that used this buffer last has left shared memory
+      // The slot's previous chunk is kRing chunks back; at most kRing - 2 newer store groups have
+      // been committed since, so when no more than that many are unread the slot is free.
+      if (lane == 0) bulk_wait_read<kRing - 2>();
       __syncwarp();
       if (lane == 0 && valid > 0) {
         mbar_arrive_expect_tx(bar, valid * chunk_row_bytes);
         bulk_load(buf, src + static_cast<long long>(r0) * row_bytes + u0 * 256, valid * chunk_row_bytes, bar);
       }
-      if (valid < rpc) {  // rows beyond the logical count travel as exact zeros
+      if (valid < rpc) {
         for (int o = valid * chunk_row_bytes + lane * 16; o < rpc * chunk_row_bytes; o += 512)
           asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(buf + o), "r"(0u) : "memory");
         fence_proxy_async_shared();
       }
       __syncwarp();
-      if (lane == 0) {
-        bool ok = true;
-        if (valid > 0) {
-          ok = mbar_wait(bar, loads[b] & 1, w, 40);
-          ++loads[b];
-        }
-        if (ok) {
-          for (int r = 0; r < rpc; ++r) {
-            char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
-            if (P.num_in == 1) {
-              bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
-                         chunk_row_bytes);
-            } else {
-              for (int u = 0; u < upp; ++u) {
-                const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
-                bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
-              }
+    };
+    // Wait for the chunk's load and hand its rows to the copy engine.
+    auto finish = [&](int c) {
+      if (lane != 0) return;
+      int r0, u0, valid;
+      geometry(c, r0, u0, valid);
+      const int b = static_cast<int>((seq + c) % kRing);
+      const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
+      bool ok = true;
+      if (valid > 0) {
+        ok = mbar_wait(bar, (parity >> b) & 1u, w, 40);
+        parity ^= 1u << b;
+      }
+      if (ok) {
+        for (int r = 0; r < rpc; ++r) {
+          char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
+          if (P.num_in == 1) {
+            bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
+                       chunk_row_bytes);
+          } else {
+            for (int u = 0; u < upp; ++u) {
+              const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
+              bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
             }
           }
         }
-        bulk_commit();
       }
-      ++issued;
+      bulk_commit();
+    };
+    start(0);
+    for (int c = 0; c < chunks_per_job; ++c) {
+      if (c + 1 < chunks_per_job) start(c + 1);
+      finish(c);
     }
+    seq += static_cast<uint32_t>(chunks_per_job);
     if (lane == 0) {
       // All of this job's bulk stores have been performed; the release makes them visible to
       // whoever acquires the counter.
@@ -314,21 +368,18 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
       }
     }
     w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
-  };
-  // Two phases (as in fused_gemm_a2a_kernels.py:358-380): every pusher warp works on the first two
-  // raster groups, which the GEMM cannot start without; afterwards only `push_warps` warps per CTA
-  // continue, enough to stay ahead of the GEMM without saturating the NVLink egress queue that
-  // the GEMM's own loads share.
-  const long long first_jobs =
-      min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
-  for (long long job = blockIdx.x * kPusherWarps + pusher; job < first_jobs && !w.dead;
-       job += static_cast<long long>(gridDim.x) * kPusherWarps)
-    do_job(job);
-  if (pusher < P.push_warps)
-    for (long long job = first_jobs + blockIdx.x * P.push_warps + pusher; job < num_jobs && !w.dead;
-         job += static_cast<long long>(gridDim.x) * P.push_warps)
-      do_job(job);
+  }
   if (lane == 0) bulk_wait_all();
+  ring.seq = seq;
+  ring.parity = parity;
+}
+
+// Jobs of the first raster groups, which the GEMM cannot start without: every pusher warp of every
+// CTA works on them (as in fused_gemm_a2a_kernels.py:358-380). What follows is the steady phase.
+__device__ __forceinline__ long long first_phase_jobs(const GemmParams& P) {
+  const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
+  const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
+  return min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -460,7 +511,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel. blockDim = 192 (local, push) or 320 (recv: + 4 pusher warps). Grid = 2 * pairs.
+// The kernel. blockDim = 192 (local, push), 320 (recv: + 4 pusher warps) or 384 (MXFP8 recv: + 2
+// quantizer warps). Grid = 2 * pairs.
 // ---------------------------------------------------------------------------------------------
 template <bool kMx>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + kPusherWarps + kQuantWarps), 1)
@@ -488,7 +540,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   const int pair = blockIdx.x >> 1;
   const int pairs = gridDim.x >> 1;
   const int total_tiles = P.m_tiles * P.n_tiles;
-  const bool gemm_on = (P.roles & 1) != 0;
+  const int total_units = total_tiles * max(1, P.k_splits);
+  // recv mode may set the last `push_pairs` CTA pairs aside: they run no GEMM role and all of
+  // their warps push for the whole kernel, so that the copy engine and the memory ports of the
+  // SMs that compute carry GEMM traffic only once the first raster groups are out.
+  const int push_pairs = P.mode == kRecv ? min(P.push_pairs, pairs - 1) : 0;
+  const int gemm_pairs = pairs - push_pairs;
+  const bool dedicated = pair >= gemm_pairs;
+  const bool gemm_role = (P.roles & 1) != 0;
+  const bool gemm_on = gemm_role && !dedicated;
+  const uint32_t ded_bufs = smem_base;  // pushing-only CTA: kDedWarps rings in the unused stages
+  const uint32_t ded_bar0 = smem_base + kDedWarps * kDedRing * kPushBufBytes;
   const int stages = P.stages;
 
   WaitCtx w{P.status, P.timeout_ns, abort_word, false};
@@ -503,6 +565,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       mbar_init(tempty0 + 8 * i, 8);  // 4 epilogue warps x 2 CTAs
     }
     for (int i = 0; i < 2 * kPusherWarps; ++i) mbar_init(push_bar0 + 8 * i, 1);
+    if (dedicated)
+      for (int i = 0; i < kDedWarps * kDedRing; ++i) mbar_init(ded_bar0 + 8 * i, 1);
     asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_word), "r"(0u) : "memory");
     fence_mbar_init();
   }
@@ -521,7 +585,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
-  if (warp == 0) {
+  if (dedicated && warp < kDedWarps) {
+    // ------------------------------------------------------------------ CTA that only pushes
+    if ((P.roles & 2) != 0) {
+      const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
+      const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
+      const long long first_jobs = first_phase_jobs(P);
+      if (warp >= kGemmWarps) {
+        const int pusher = warp - kGemmWarps;
+        PushRing first;
+        run_pushers<2>(P, blockIdx.x * kPusherWarps + pusher, first_jobs,
+                       static_cast<long long>(gridDim.x) * kPusherWarps, lane,
+                       push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, first, w);
+      }
+      const int ded_cta = static_cast<int>(blockIdx.x) - 2 * gemm_pairs;
+      PushRing steady;
+      run_pushers<kDedRing>(P, first_jobs + ded_cta * kDedWarps + warp, num_jobs,
+                            static_cast<long long>(2 * push_pairs) * kDedWarps, lane,
+                            ded_bufs + warp * kDedRing * kPushBufBytes, ded_bar0 + 8 * kDedRing * warp,
+                            steady, w);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0 && gemm_on) {
       const uint32_t tx_bytes =
@@ -529,8 +613,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       const int b_half = P.bn >> 1;
       int s = 0;
       uint32_t ph = 0;
-      for (int t = pair; t < total_tiles && !w.dead; t += pairs) {
-        int m, n;
+      for (int u = pair; u < total_units && !w.dead; u += gemm_pairs) {
+        int t, kt0, kt1, m, n;
+        unit_coords(P, u, total_tiles, t, kt0, kt1);
         tile_coords(P, t, m, n);
         const int a_row0 = m * 256 + static_cast<int>(cta_rank) * kTileM;
         const int b_row0 = b_row0_of(P, n) + static_cast<int>(cta_rank) * b_half;
@@ -542,7 +627,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
           if (P.progress != nullptr && P.epoch != nullptr)
             atomicMax(P.progress, (static_cast<int>(*P.epoch & 0x3fff) << 17) + m);
         }
-        for (int kt = 0; kt < P.k_tiles; ++kt) {
+        for (int kt = kt0; kt < kt1; ++kt) {
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, w, 11)) break;
           const uint32_t a_dst = smem_base + s * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
@@ -589,11 +674,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       const uint32_t a_step = P.a_mn ? 128u : 2u, b_step = P.b_mn ? 128u : 2u;
       int s = 0, as = 0;
       uint32_t ph = 0, aph = 0;
-      for (int t = pair; t < total_tiles && !w.dead; t += pairs) {
+      for (int u = pair; u < total_units && !w.dead; u += gemm_pairs) {
+        int t, kt0, kt1;
+        unit_coords(P, u, total_tiles, t, kt0, kt1);
         if (!mbar_wait(tempty0 + 8 * as, aph ^ 1, w, 20)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * P.bn;
-        for (int kt = 0; kt < P.k_tiles; ++kt) {
+        for (int kt = kt0; kt < kt1; ++kt) {
           if (!mbar_wait(full0 + 8 * s, ph, w, 21)) break;
           tc_fence_after();
           const uint32_t a_addr = smem_base + s * kStageBytes;
@@ -613,12 +700,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
             for (int k = 0; k < 4; ++k)
               mma_mxf8_pair(d_tmem, adesc + k * 2, bdesc + k * 2,
                             P.idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), sfa_t,
-                            sfb_t, (kt | k) != 0 ? 1u : 0u);
+                            sfb_t, (kt != kt0 || k != 0) ? 1u : 0u);
           } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               mma_bf16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, P.idesc,
-                            (kt | k) != 0 ? 1u : 0u);
+                            (kt != kt0 || k != 0) ? 1u : 0u);
           }
           tc_commit_pair(empty0 + 8 * s, 3);  // frees the stage in both CTAs when the MMAs retire
           if (++s == stages) {
@@ -643,8 +730,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       bool stores_pending = false;
       int as = 0;
       uint32_t aph = 0;
-      for (int t = pair; t < total_tiles; t += pairs) {
-        int m, n;
+      for (int u = pair; u < total_units; u += gemm_pairs) {
+        int t, kt0, kt1, m, n;
+        unit_coords(P, u, total_tiles, t, kt0, kt1);
         tile_coords(P, t, m, n);
         const bool ok = mbar_wait(tfull0 + 8 * as, aph, w, 30);
         // All lanes take the same branch: the barrier state is CTA-wide and aborts are sticky.
@@ -670,12 +758,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
     // ------------------------------------------------------------------ pusher warps (recv mode)
     if (P.mode == kRecv && (P.roles & 2) != 0) {
       const int pusher = warp - kGemmWarps;
-      run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, w);
+      const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
+      const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
+      const long long first_jobs = first_phase_jobs(P);
+      const uint32_t bufs = push_bufs + pusher * 2 * kPushBufBytes, pbar = push_bar0 + 16 * pusher;
+      PushRing ring;
+      run_pushers<2>(P, blockIdx.x * kPusherWarps + pusher, first_jobs,
+                     static_cast<long long>(gridDim.x) * kPusherWarps, lane, bufs, pbar, ring, w);
+      // Steady phase. Without pushing-only CTAs, `push_warps` warps of every CTA continue: enough
+      // to stay ahead of the GEMM without saturating the NVLink egress queue that the GEMM's own
+      // loads share. With them, the CTAs that compute are done pushing here.
+      if (push_pairs == 0 && pusher < P.push_warps)
+        run_pushers<2>(P, first_jobs + blockIdx.x * P.push_warps + pusher, num_jobs,
+                       static_cast<long long>(gridDim.x) * P.push_warps, lane, bufs, pbar, ring, w);
     }
   } else {
     // ------------------------------------------------------------------ quantizer warps (MXFP8 recv)
     if constexpr (kMx) {
-      if (P.mode == kRecv && gemm_on) run_quantizers(P, warp - kGemmWarps - kPusherWarps, lane, w);
+      if (P.mode == kRecv && gemm_role) run_quantizers(P, warp - kGemmWarps - kPusherWarps, lane, w);
     }
   }
 

@@ -385,9 +385,12 @@ class _FusedOutput(torch.autograd.Function):
         dy = dy.contiguous()
         comm.barrier()
         workspace.run_push(dy, weight, True, 1)
-        comm.barrier()
+        # The weight and bias gradients need nothing from the peers: they run between the push and
+        # the barrier that waits for everybody's tiles, so a rank that finished its push early
+        # computes instead of idling and the remote stores have landed by the time it arrives.
         dw = _weight_grad(module.weight, dy, o_seq, workspace.precision, comm.status)
         db = _bias_grad(module.bias, dy, module.accumulate_bias_grad) if ctx.has_bias else None
+        comm.barrier()
         do, = resize_rank_rows(workspace.heads, comm.p, tokens, copy=True)
         return do.view(-1, do.shape[1] // module.head_dim, module.head_dim), dw, db, None, None, None
 
