@@ -691,5 +691,30 @@ def main():
         run_gpu_arm(args)
 
 
+def guarded_main():
+    """Ranks of a fused multi-GPU run write into each other's buffers, and a rank that exits frees
+    its own. So a rank that fails does not leave at once: its kernels finish, then it stays (buffers
+    mapped) until the peers' bounded device waits (FGA_TIMEOUT_S, default 20 s) have run out and
+    their sticky error status keeps later launches from writing here. Then it exits non-zero."""
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        if int(os.environ.get('WORLD_SIZE', '1')) > 1:
+            try:
+                import torch
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+            except Exception:
+                pass
+            time.sleep(float(os.environ.get('FGA_TIMEOUT_S', '20')) + 2.0)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1)
+
+
 if __name__ == '__main__':
-    main()
+    guarded_main()

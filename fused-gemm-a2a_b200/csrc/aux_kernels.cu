@@ -22,6 +22,9 @@ __global__ void barrier_kernel(long long* flags, const long long* peer_flags, in
                                int bump, int* counters, int count, int* epoch_out, int* status,
                                unsigned long long timeout_ns) {
   const int lane = threadIdx.x;
+  // A recorded device error is sticky: a peer that never answered may be gone together with its
+  // memory, so nothing is written to any peer until the host has cleared the status word.
+  if (ld_relaxed_sys_s32(status) != 0) return;
   if (bump) {
     for (int i = lane; i < count; i += 32) counters[i] = 0;
     __syncwarp();

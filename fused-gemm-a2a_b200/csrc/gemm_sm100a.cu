@@ -102,22 +102,31 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cu
 // Shares of the K steps per output tile for an FP32 gradient GEMM. A persistent grid of `pairs`
 // CTA pairs runs ceil(tiles / pairs) waves and the last one may be mostly empty (256 tiles on 74
 // pairs: 3.46 waves, 86 % efficiency). Cutting K multiplies the work units and fills the last wave;
-// every unit adds its partial tile with bulk reductions, so no second pass is needed. The smallest
-// split count that reaches 97 % wave efficiency is taken, each share keeping at least 32 K steps.
+// every unit adds its partial tile with bulk reductions, so no second pass is needed.
+// FGA_WGRAD_SPLITS selects it: unset or 1 = one unit per tile (the default), N = N shares,
+// "auto" = the smallest count that reaches 97 % wave efficiency. A share keeps at least 32 K steps.
 static int choose_k_splits(long long tiles, int k_tiles, int pairs) {
-  const int forced = env_int("FGA_WGRAD_SPLITS", 0);
+  const char* v = getenv("FGA_WGRAD_SPLITS");
+  if (v == nullptr || *v == '\0') return 1;
+  const bool automatic = strcmp(v, "auto") == 0;
+  const int forced = automatic ? 0 : atoi(v);
+  if (!automatic && forced <= 1) return 1;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= 8; ++s) {
     if (s > 1 && k_tiles / s < 32) break;
+    if (!automatic) {
+      best = s;  // the largest allowed count up to the forced one
+      if (s == forced) break;
+      continue;
+    }
     const long long units = tiles * s;
     const double eff = static_cast<double>(units) / (static_cast<double>((units + pairs - 1) / pairs) * pairs);
-    if (s == forced) return s;
     if (eff > best_eff + 1e-9) {
       best_eff = eff;
       best = s;
     }
-    if (forced == 0 && eff >= 0.97) return s;
+    if (eff >= 0.97) break;
   }
   return best;
 }

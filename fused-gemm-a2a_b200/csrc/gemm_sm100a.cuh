@@ -227,13 +227,141 @@ __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
 // buffer, columns in Megatron order [head][q|k|v|g][D], rows past src_rows as zeros; then one
 // release-increment of d's counter for that row block (fused_gemm_a2a_kernels.py:291-380 is the
 // reference's register-copy version). Here one lane per warp drives the TMA unit: a chunk of up
-// to 4 KiB is bulk-loaded from local memory into a slot of the warp's ring of shared buffers and
+// to 4 KiB is bulk-loaded from local memory into one of the warp's two shared buffers and
 // bulk-stored to the peer in 256-byte head units (or whole rows when the columns are contiguous),
-// so the data never passes through registers and remote stores queue in the copy engine. The load
-// of the next chunk is started before the stores of the current one are issued.
-//
-// The warp takes jobs job_begin, job_begin + job_stride, ... < job_end. kRing = slots in its ring
-// (buf0 / bar0: kRing buffers of kPushBufBytes and kRing mbarriers).
+// so the data never passes through registers and remote stores queue in the copy engine.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane, uint32_t buf0,
+                                            uint32_t bar0, bool steady, WaitCtx& w) {
+  const int hpr = P.heads_per_rank;
+  const int row_bytes = hpr * 256;
+  const int sub_rows = kTileM / P.split;
+  const int upp = P.push_units, rpc = P.push_rows;
+  const int pieces_per_row = hpr / upp;
+  const int chunk_row_bytes = upp * 256;
+  const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
+  const int jobs_per_block = P.num_in * P.p * P.split;
+  const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
+  const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
+  const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
+  uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
+  uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
+  auto do_job = [&](long long job) {
+    const int mi = static_cast<int>(job / jobs_per_block);
+    int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
+    const int q = rest % P.split;
+    rest /= P.split;
+    const int d = (rest % P.p + P.rank) % P.p;
+    const int t = rest / P.p;
+    const int row0 = mi * kTileM + q * sub_rows;
+    if (paced) {
+      // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
+      // the same schedule, so the peers consume at about this rank's pace; pushing faster only
+      // saturates the NVLink egress queue, behind which the GEMM's own loads then wait.
+      const int need = ((mi >> 1) / P.group_m - P.push_lead) * P.group_m;  // pair tile that must have started
+      if (need > 0 && lane == 0) {
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t it = 0;
+        while (ld_relaxed_sys_s32(P.progress) - base < need) {
+          nanosleep(200);
+          if ((++it & 0xff) == 0) {
+            if (should_abort(w)) break;
+            if (globaltimer_ns() - t0 > w.timeout_ns) {
+              report(w, kErrCounterTimeout, 41, mi);
+              break;
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+    const char* src = static_cast<const char*>(P.src[t]) +
+                      (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
+    char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
+    for (int c = 0; c < chunks_per_job; ++c) {
+      int r0, u0;
+      if (pieces_per_row == 1) {
+        r0 = c * rpc;
+        u0 = 0;
+      } else {
+        r0 = c / pieces_per_row;
+        u0 = (c - r0 * pieces_per_row) * upp;
+      }
+      const int b = issued & 1;
+      const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
+      const int valid = max(0, min(rpc, P.src_rows - (row0 + r0)));  // rows that exist in the source
+      if (lane == 0) bulk_wait_read<1>();  // the group that used this buffer last has left shared memory
+      __syncwarp();
+      if (lane == 0 && valid > 0) {
+        mbar_arrive_expect_tx(bar, valid * chunk_row_bytes);
+        bulk_load(buf, src + static_cast<long long>(r0) * row_bytes + u0 * 256, valid * chunk_row_bytes, bar);
+      }
+      if (valid < rpc) {  // rows beyond the logical count travel as exact zeros
+        for (int o = valid * chunk_row_bytes + lane * 16; o < rpc * chunk_row_bytes; o += 512)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(buf + o), "r"(0u) : "memory");
+        fence_proxy_async_shared();
+      }
+      __syncwarp();
+      if (lane == 0) {
+        bool ok = true;
+        if (valid > 0) {
+          ok = mbar_wait(bar, loads[b] & 1, w, 40);
+          ++loads[b];
+        }
+        if (ok) {
+          for (int r = 0; r < rpc; ++r) {
+            char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
+            if (P.num_in == 1) {
+              bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
+                         chunk_row_bytes);
+            } else {
+              for (int u = 0; u < upp; ++u) {
+                const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
+                bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
+              }
+            }
+          }
+        }
+        bulk_commit();
+      }
+      ++issued;
+    }
+    if (lane == 0) {
+      // All of this job's bulk stores have been performed; the release makes them visible to
+      // whoever acquires the counter.
+      bulk_wait_all();
+      fence_proxy_async_all();
+      if (!w.dead) {
+        int* ctr = reinterpret_cast<int*>(P.peer_counters[d]) + mi;
+        if (P.push_flags & 1)
+          red_relaxed_sys_add(ctr, 1);
+        else
+          red_release_sys_add(ctr, 1);
+      }
+    }
+    w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
+  };
+  // Two phases (as in fused_gemm_a2a_kernels.py:358-380): every pusher warp works on the first two
+  // raster groups, which the GEMM cannot start without; afterwards only `push_warps` warps per CTA
+  // continue, enough to stay ahead of the GEMM without saturating the NVLink egress queue that
+  // the GEMM's own loads share. `steady` is false when CTAs that only push take that part over.
+  const long long first_jobs =
+      min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
+  for (long long job = blockIdx.x * kPusherWarps + pusher; job < first_jobs && !w.dead;
+       job += static_cast<long long>(gridDim.x) * kPusherWarps)
+    do_job(job);
+  if (steady && pusher < P.push_warps)
+    for (long long job = first_jobs + blockIdx.x * P.push_warps + pusher; job < num_jobs && !w.dead;
+         job += static_cast<long long>(gridDim.x) * P.push_warps)
+      do_job(job);
+  if (lane == 0) bulk_wait_all();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same job loop for a CTA that only pushes (GemmParams::push_pairs): the warp takes jobs
+// job_begin, job_begin + job_stride, ... < job_end and owns a ring of kRing shared buffers (buf0)
+// and mbarriers (bar0), so that the load of the next chunk is in flight while the stores of the
+// current one are issued.
 // ---------------------------------------------------------------------------------------------
 struct PushRing {
   uint32_t seq = 0;     // chunks started on this ring (selects the slot)
@@ -241,7 +369,7 @@ struct PushRing {
 };
 
 template <int kRing>
-__device__ __noinline__ void run_pushers(const GemmParams& P, long long job_begin, long long job_end,
+__device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job_begin, long long job_end,
                                          long long job_stride, int lane, uint32_t buf0, uint32_t bar0,
                                          PushRing& ring, WaitCtx& w) {
   static_assert(kRing >= 2 && kRing <= 8, "ring depth");
@@ -553,7 +681,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   const uint32_t ded_bar0 = smem_base + kDedWarps * kDedRing * kPushBufBytes;
   const int stages = P.stages;
 
-  WaitCtx w{P.status, P.timeout_ns, abort_word, false};
+  // A device error recorded by an earlier kernel is sticky: every role starts out aborted, so no
+  // peer memory is touched (the peer that never answered may be gone) until the host clears it.
+  WaitCtx w{P.status, P.timeout_ns, abort_word, ld_relaxed_sys_s32(P.status) != 0};
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
@@ -593,14 +723,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       const long long first_jobs = first_phase_jobs(P);
       if (warp >= kGemmWarps) {
         const int pusher = warp - kGemmWarps;
-        PushRing first;
-        run_pushers<2>(P, blockIdx.x * kPusherWarps + pusher, first_jobs,
-                       static_cast<long long>(gridDim.x) * kPusherWarps, lane,
-                       push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, first, w);
+        run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, false, w);
       }
       const int ded_cta = static_cast<int>(blockIdx.x) - 2 * gemm_pairs;
       PushRing steady;
-      run_pushers<kDedRing>(P, first_jobs + ded_cta * kDedWarps + warp, num_jobs,
+      run_pushers_ring<kDedRing>(P, first_jobs + ded_cta * kDedWarps + warp, num_jobs,
                             static_cast<long long>(2 * push_pairs) * kDedWarps, lane,
                             ded_bufs + warp * kDedRing * kPushBufBytes, ded_bar0 + 8 * kDedRing * warp,
                             steady, w);
@@ -758,19 +885,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
     // ------------------------------------------------------------------ pusher warps (recv mode)
     if (P.mode == kRecv && (P.roles & 2) != 0) {
       const int pusher = warp - kGemmWarps;
-      const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
-      const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
-      const long long first_jobs = first_phase_jobs(P);
-      const uint32_t bufs = push_bufs + pusher * 2 * kPushBufBytes, pbar = push_bar0 + 16 * pusher;
-      PushRing ring;
-      run_pushers<2>(P, blockIdx.x * kPusherWarps + pusher, first_jobs,
-                     static_cast<long long>(gridDim.x) * kPusherWarps, lane, bufs, pbar, ring, w);
-      // Steady phase. Without pushing-only CTAs, `push_warps` warps of every CTA continue: enough
-      // to stay ahead of the GEMM without saturating the NVLink egress queue that the GEMM's own
-      // loads share. With them, the CTAs that compute are done pushing here.
-      if (push_pairs == 0 && pusher < P.push_warps)
-        run_pushers<2>(P, first_jobs + blockIdx.x * P.push_warps + pusher, num_jobs,
-                       static_cast<long long>(gridDim.x) * P.push_warps, lane, bufs, pbar, ring, w);
+      // With CTAs that only push, the ones that compute stop pushing after the first raster groups.
+      run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher,
+                  push_pairs == 0, w);
     }
   } else {
     // ------------------------------------------------------------------ quantizer warps (MXFP8 recv)

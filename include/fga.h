@@ -14,7 +14,10 @@
  *     pointers live on.
  *   - `status` is a caller-owned int[4] in device memory, zeroed once by the caller. A kernel
  *     whose bounded wait expires writes {code, where, detail, 0} (FgaDeviceError) and returns;
- *     the context stays usable. Kernels never clear it.
+ *     the context stays usable. Kernels never clear it, and the error is sticky: while status[0]
+ *     is non-zero, fga_barrier and the fused GEMMs return at once without touching any peer's
+ *     memory (the peer that did not answer may have exited and unmapped it). The host reads the
+ *     word, tears the group down or repairs it, and zeroes the word before it launches again.
  *   - all matrices are row-major; BF16 is passed as 16-bit words.
  */
 #ifndef FGA_H_

@@ -3,9 +3,18 @@
 Every rank runs the public modules on its own GPU; inputs of all ranks are gathered so that each
 rank can evaluate the CPU oracle for the whole CP group and compare its own outputs, gradients and
 the raw transport buffers. Exits non-zero on any mismatch or device-side timeout.
+
+Ranks leave together. A rank that exits frees the buffers its peers write into, and a peer that
+went on to its next launch would then store into unmapped memory. So a failed comparison is
+recorded, not raised; after every case the ranks agree (one all-reduce) whether anybody failed and,
+if so, all stop at that point with nothing in flight. An unexpected exception keeps the process,
+and with it its buffers, alive until the peers' bounded waits have run out.
 """
+import contextlib
 import os
 import sys
+import time
+import traceback
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 for path in (ROOT, os.path.join(ROOT, 'fused-gemm-a2a_b200')):
@@ -29,6 +38,33 @@ def close(actual, expected, what):
     assert torch.linalg.norm(actual - expected) <= 2e-3 * torch.linalg.norm(expected) + 1e-6, f'{what}: Frobenius'
 
 
+class Agreement:
+    """Soft assertions with a collective verdict."""
+
+    def __init__(self, dev):
+        self.dev, self.failures = dev, []
+
+    @contextlib.contextmanager
+    def checks(self, label):
+        try:
+            yield
+        except AssertionError as error:
+            self.failures.append(f'{label}: {error}')
+
+    def settle(self, label):
+        """All ranks learn whether any rank failed; if so, all of them stop here."""
+        flag = torch.tensor([len(self.failures)], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if flag.item() == 0:
+            return
+        for failure in self.failures:
+            print(f'[rank {dist.get_rank()}] FAIL {failure}', flush=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(1)
+
+
 def gather(t):
     parts = [torch.empty_like(t) for _ in range(dist.get_world_size())]
     dist.all_gather(parts, t.contiguous())
@@ -44,6 +80,7 @@ def main():
     hidden, heads = 1024, 8
     d = hidden // heads
     checks = 0
+    verdict = Agreement(dev)
     for gate, with_bias, bias_in_gemm in ((False, False, False), (True, True, False), (False, True, True)):
         segments = 4 if gate else 3
         g = torch.Generator().manual_seed(4321)  # replicated parameters
@@ -69,29 +106,33 @@ def main():
             y = proj(o, ws)
             do, dwo, *dbo = torch.autograd.grad(y, [o, wo_d] + ([bo_d] if with_bias else []), dy)
             torch.cuda.synchronize()
-            ws.comm.check_status()
-            # exact transport: the QKV receive buffer still holds this rank's dY, the output receive
-            # buffer this rank's sequence-side O, pad rows zero
             all_grads = list(zip(*[gather(t) for t in grads]))       # [rank][segment]
             all_o = gather(o.detach())
-            cap = ws._view(tokens, segments).capacity
-            want_dy = oracle.qkv_recv_buffer(all_grads, rank, cap)
-            assert torch.equal(ws._view(tokens, segments).recv.cpu(), want_dy), 'QKV dgrad transport'
-            assert torch.equal(ws._view(tokens, 1).recv.cpu(), oracle.out_recv_buffer(all_o, rank, cap)), 'output transport'
             xs, dys = gather(x.detach()), gather(dy)
-            want_outs = oracle.qkv_forward(xs)[rank]
-            for name, got, want in zip('qkvg', outs, want_outs):
-                close(got, want, f'{name} tokens={tokens}')
-            rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
-            close(dx, rdx, 'dx')
-            close(dwq, rdw, 'dW_qkv')
-            close(y, oracle.out_forward(all_o)[rank], 'y')
-            rdos, rparams = oracle.out_backward(all_o, dys)
-            close(do, rdos[rank], 'dO')
-            close(dwo, rparams[rank][0], 'dW_o')
-            if with_bias:
-                close(dbq[0], rdb, 'dbias_qkv')
-                close(dbo[0], rparams[rank][1], 'dbias_o')
+            label = f'gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm} tokens={tokens}'
+            with verdict.checks(label):
+                assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
+                # exact transport: the QKV receive buffer still holds this rank's dY, the output
+                # receive buffer this rank's sequence-side O, pad rows zero
+                cap = ws._view(tokens, segments).capacity
+                want_dy = oracle.qkv_recv_buffer(all_grads, rank, cap)
+                assert torch.equal(ws._view(tokens, segments).recv.cpu(), want_dy), 'QKV dgrad transport'
+                assert torch.equal(ws._view(tokens, 1).recv.cpu(),
+                                   oracle.out_recv_buffer(all_o, rank, cap)), 'output transport'
+                want_outs = oracle.qkv_forward(xs)[rank]
+                for name, got, want in zip('qkvg', outs, want_outs):
+                    close(got, want, f'{name} tokens={tokens}')
+                rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
+                close(dx, rdx, 'dx')
+                close(dwq, rdw, 'dW_qkv')
+                close(y, oracle.out_forward(all_o)[rank], 'y')
+                rdos, rparams = oracle.out_backward(all_o, dys)
+                close(do, rdos[rank], 'dO')
+                close(dwo, rparams[rank][0], 'dW_o')
+                if with_bias:
+                    close(dbq[0], rdb, 'dbias_qkv')
+                    close(dbo[0], rparams[rank][1], 'dbias_o')
+            verdict.settle(label)
             checks += 1
         if rank == 0:
             print(f'PASS gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm}', flush=True)
@@ -126,21 +167,24 @@ def main():
         y = proj(o, ws)
         do, dwo = torch.autograd.grad(y, [o, wo_d], dy)
         torch.cuda.synchronize()
-        ws.comm.check_status()
         xs, dys, all_o = gather(x.detach()), gather(dy), gather(o.detach())
         all_grads = list(zip(*[gather(t) for t in grads]))
-        plain = UlyssesOracle(p, hidden, heads, 3)
-        for seg in range(3):
-            want = torch.cat([mm(xr, wq).view(tokens, heads, 3, d)[:, rank * hpr:(rank + 1) * hpr, seg] for xr in xs])
-            close(outs[seg], want, f'mxfp8 segment {seg}')
-        dyq = plain.qkv_recv_buffer(all_grads, rank)
-        close(dx, mm(dyq, wq.t()), 'mxfp8 dx')
-        close(dwq, mm(dyq.t(), xs[rank].t()), 'mxfp8 dW_qkv')
-        o_seq = plain.out_recv_buffer(all_o, rank)
-        close(y, mm(o_seq, wo), 'mxfp8 y')
-        full_do = torch.cat([mm(dyr, wo.t())[:, rank * hpr * d:(rank + 1) * hpr * d] for dyr in dys])
-        close(do, full_do.view(p * tokens, hpr, d), 'mxfp8 dO')
-        close(dwo, mm(dys[rank].t(), o_seq.t()), 'mxfp8 dW_o')
+        with verdict.checks(f'mxfp8 tokens={tokens}'):
+            assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
+            plain = UlyssesOracle(p, hidden, heads, 3)
+            for seg in range(3):
+                want = torch.cat([mm(xr, wq).view(tokens, heads, 3, d)[:, rank * hpr:(rank + 1) * hpr, seg]
+                                  for xr in xs])
+                close(outs[seg], want, f'mxfp8 segment {seg}')
+            dyq = plain.qkv_recv_buffer(all_grads, rank)
+            close(dx, mm(dyq, wq.t()), 'mxfp8 dx')
+            close(dwq, mm(dyq.t(), xs[rank].t()), 'mxfp8 dW_qkv')
+            o_seq = plain.out_recv_buffer(all_o, rank)
+            close(y, mm(o_seq, wo), 'mxfp8 y')
+            full_do = torch.cat([mm(dyr, wo.t())[:, rank * hpr * d:(rank + 1) * hpr * d] for dyr in dys])
+            close(do, full_do.view(p * tokens, hpr, d), 'mxfp8 dO')
+            close(dwo, mm(dys[rank].t(), o_seq.t()), 'mxfp8 dW_o')
+        verdict.settle(f'mxfp8 tokens={tokens}')
     if rank == 0:
         print('PASS mxfp8', flush=True)
 
@@ -189,19 +233,21 @@ def main():
         dist.barrier()
         graph.replay()
         torch.cuda.synchronize()
-        ws.comm.check_status()
         xs, all_o, dys = gather(sx.detach()), gather(so.detach()), gather(sdy)
         all_grads = list(zip(*[gather(t) for t in sg]))
-        q, k, v, dx, dw, y, do, dwo = outputs
-        for got, want in zip((q, k, v), oracle.qkv_forward(xs)[rank]):
-            close(got, want, f'replay {replay} qkv')
-        rdx, rdw, _ = oracle.qkv_backward(xs, all_grads)[rank]
-        close(dx, rdx, 'replay dx')
-        close(dw, rdw, 'replay dW_qkv')
-        close(y, oracle.out_forward(all_o)[rank], 'replay y')
-        rdos, rparams = oracle.out_backward(all_o, dys)
-        close(do, rdos[rank], 'replay dO')
-        close(dwo, rparams[rank][0], 'replay dW_o')
+        with verdict.checks(f'graph replay {replay}'):
+            assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
+            q, k, v, dx, dw, y, do, dwo = outputs
+            for got, want in zip((q, k, v), oracle.qkv_forward(xs)[rank]):
+                close(got, want, f'replay {replay} qkv')
+            rdx, rdw, _ = oracle.qkv_backward(xs, all_grads)[rank]
+            close(dx, rdx, 'replay dx')
+            close(dw, rdw, 'replay dW_qkv')
+            close(y, oracle.out_forward(all_o)[rank], 'replay y')
+            rdos, rparams = oracle.out_backward(all_o, dys)
+            close(do, rdos[rank], 'replay dO')
+            close(dwo, rparams[rank][0], 'replay dW_o')
+        verdict.settle(f'graph replay {replay}')
     if rank == 0:
         print(f'PASS cuda graph replay; {checks} eager configurations checked on {p} GPUs', flush=True)
     torch.cuda.synchronize()
@@ -210,4 +256,18 @@ def main():
 
 
 if __name__ == '__main__':
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:
+        # Not a comparison failure: this rank cannot tell where its peers are. Its kernels finish,
+        # then it keeps its buffers mapped until the peers' bounded waits (FGA_TIMEOUT_S) have
+        # expired and their sticky error status has stopped further launches from writing here.
+        traceback.print_exc()
+        try:
+            torch.cuda.synchronize()
+        except Exception:
+            pass
+        time.sleep(float(os.environ.get('FGA_TIMEOUT_S', '10')) + 2.0)
+        os._exit(1)

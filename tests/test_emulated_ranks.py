@@ -85,18 +85,6 @@ def test_output_dgrad_push_routes_columns_to_their_owner(native, p, hidden, head
         close(bufs[d], want[d], f'dest {d}')
 
 
-@pytest.mark.parametrize('push_pairs', [0, 3, 200])
-@pytest.mark.parametrize('p,hidden,heads,tokens,num_in', [(2, 512, 4, 1100, 3), (4, 1024, 8, 1300, 1)])
-def test_receive_steady_phase_and_pushing_only_ctas(native, monkeypatch, p, hidden, heads, tokens, num_in,
-                                                    push_pairs):
-    # One row tile per raster group: the first phase covers two of the five or six row tiles and
-    # the rest goes through the steady phase, on every CTA (0) or on CTA pairs that only push
-    # (3; 200 is clamped so that one pair still computes).
-    monkeypatch.setenv('FGA_GROUP_M_RECV', '1')
-    monkeypatch.setenv('FGA_PUSH_PAIRS', str(push_pairs))
-    test_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in)
-
-
 @pytest.mark.parametrize('p,hidden,heads,tokens,num_in', [
     (2, 512, 4, 300, 1), (2, 512, 4, 300, 3), (4, 1024, 8, 129, 4), (8, 1024, 8, 256, 3), (4, 512, 4, 1, 1)])
 def test_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in):

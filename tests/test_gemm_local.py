@@ -56,39 +56,6 @@ def test_weight_gradient_layout_fp32(native, m, n, k, accumulate):
     assert (c - ref).abs().max() <= 1e-4 * ref.abs().max()
 
 
-@pytest.mark.parametrize('splits', ['', '1', '4', '8'])
-@pytest.mark.parametrize('accumulate', [False, True])
-def test_weight_gradient_split_along_tokens(native, monkeypatch, splits, accumulate):
-    """A long token axis is cut into shares that add into the FP32 output (chosen by the library,
-    or forced). The output is a column window of a wider matrix: a plain store zero-fills exactly
-    that window first and the neighbouring columns keep their contents."""
-    if splits:
-        monkeypatch.setenv('FGA_WGRAD_SPLITS', splits)
-    dev = torch.device('cuda', 0)
-    m, n, k, ldc = 300, 256, 16384, 384
-    g = torch.Generator().manual_seed(11)
-    dy = torch.randn(k, m, generator=g).to(torch.bfloat16).to(dev)
-    x = (torch.randn(k, n, generator=g) / 8).to(torch.bfloat16).to(dev)
-    start = torch.randn(m, ldc, generator=g).to(dev)
-    wide = start.clone()
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
-    # operands need 16-byte aligned rows: pad the token-major dY to a multiple of 8 columns
-    lda = (m + 7) // 8 * 8
-    dy_pad = torch.zeros(k, lda, dtype=torch.bfloat16, device=dev)
-    dy_pad[:, :m] = dy
-    rc = native.fga_gemm_local(dy_pad.data_ptr(), 1, x.data_ptr(), 1, m, n, k, lda, n,
-                               wide.data_ptr() + 64 * 4, ldc, 1, int(accumulate), status.data_ptr(),
-                               TIMEOUT_NS, torch.cuda.current_stream().cuda_stream)
-    assert rc == 0, native.fga_last_error()
-    torch.cuda.synchronize()
-    assert status.tolist() == [0, 0, 0, 0]
-    ref = dy.float().t() @ x.float()
-    if accumulate:
-        ref = ref + start[:, 64:64 + n]
-    assert (wide[:, 64:64 + n] - ref).abs().max() <= 1e-4 * ref.abs().max()
-    assert torch.equal(wide[:, :64], start[:, :64]) and torch.equal(wide[:, 64 + n:], start[:, 64 + n:])
-
-
 def test_large_square_matches_reference(native):
     c, ref = _run(native, 2048, 2048, 2048, 0, 0)
     assert torch.linalg.norm(c - ref) <= 2e-3 * torch.linalg.norm(ref)
