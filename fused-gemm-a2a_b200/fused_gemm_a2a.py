@@ -191,6 +191,12 @@ class _Comm:
             reason = _native.DEVICE_ERRORS.get(code, 'unknown device error')
             raise RuntimeError(f'Fused GEMM/A2A device error {code}: {reason} (where={where}, detail={detail})')
 
+    def clear_status(self):
+        """Zero the status word once a device error has been dealt with. The word is sticky: while
+        it holds a code, barriers and fused GEMMs of this group return at entry without touching any
+        peer's memory, because the peer that never answered may have unmapped it."""
+        self.status.zero_()
+
     @staticmethod
     def push_split(a, num_in, p):
         return push_split(a.shape[1], p, num_in, PUSH_SPLIT)
