@@ -17,6 +17,7 @@ mapped into every peer with CUDA IPC handles exchanged once over the CP group; t
 hand-written TMA/tcgen05 kernels whose epilogue (push) or pusher warps (receive) perform the
 all-to-all over NVLink. No kernel is compiled at run time and nothing falls back to the CPU.
 """
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -33,6 +34,14 @@ from fused_gemm_a2a_kernels import (  # noqa: F401  (re-exported: the reference'
 )
 
 __all__ = ['FusedGemmA2AWorkspace', 'FusedQKVProjection', 'FusedOutputProjection']
+
+# The reference selects between torch's GEMM + add_ and Megatron's accumulating cuBLAS extension
+# for the BF16 weight gradient (fused_gemm_a2a.py:34-40). Here both settings mean the same thing:
+# the GEMM epilogue adds straight into main_grad, so no extension is imported. The variable is
+# still validated so that a launch script written for the reference fails the same way.
+WGRAD_BACKEND = os.environ.get('FUSED_WGRAD_BACKEND', 'torch')
+if WGRAD_BACKEND not in ('torch', 'fused_accum'):
+    raise ValueError('FUSED_WGRAD_BACKEND must be torch or fused_accum')
 
 _ALIGN = 1024  # every sub-buffer of a symmetric slab starts on a 1 KiB boundary
 

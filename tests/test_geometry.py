@@ -144,3 +144,20 @@ def test_module_construction_needs_no_process_group_or_gpu_work():
         fused.FusedOutputProjection(256, 2, weight=torch.empty(256, 256, dtype=torch.bfloat16),
                                     bias=torch.empty(255, dtype=torch.bfloat16))
     assert fused.FusedQKVProjection.weight_layout == 'head_qkvg'
+
+
+def test_wgrad_backend_variable_is_validated_like_the_reference():
+    """FUSED_WGRAD_BACKEND accepts the reference's two settings (both use the accumulating
+    epilogue here) and rejects anything else at import (reference fused_gemm_a2a.py:34-36)."""
+    import os
+    import subprocess
+    import sys
+    package = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'fused-gemm-a2a_b200')
+    code = f'import sys; sys.path.insert(0, {package!r}); import fused_gemm_a2a as f; print(f.WGRAD_BACKEND)'
+    for value, ok in (('torch', True), ('fused_accum', True), ('cublas', False)):
+        run = subprocess.run([sys.executable, '-c', code], env=dict(os.environ, FUSED_WGRAD_BACKEND=value),
+                             capture_output=True, text=True, timeout=300)
+        if ok:
+            assert run.returncode == 0 and run.stdout.strip() == value, run.stderr[-500:]
+        else:
+            assert run.returncode != 0 and 'FUSED_WGRAD_BACKEND must be torch or fused_accum' in run.stderr
