@@ -267,7 +267,6 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   // queue that the GEMM's own loads share).
   P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
-  P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
   P.epoch = reinterpret_cast<const long long*>(epoch);
   P.progress = progress;
   P.push_lead = env_int("FGA_PUSH_LEAD", 0);
@@ -493,7 +492,6 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   // queue that the GEMM's own loads share).
   P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
-  P.push_flags = env_int("FGA_PUSH_FLAGS", 0);
   P.epoch = reinterpret_cast<const long long*>(epoch);
   P.progress = progress;
   P.push_lead = env_int("FGA_PUSH_LEAD", 0);

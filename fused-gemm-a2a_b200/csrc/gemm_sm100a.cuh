@@ -91,7 +91,6 @@ struct GemmParams {
   long long recv_k;                // elements per receive-buffer row
   int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
   int push_warps;                  // pusher warps that take jobs (1..kPusherWarps)
-  int push_flags;                  // bit 0: plain (non-release) counter increment after the drain
   const long long* epoch;          // a device word that grows with every invocation (barrier epoch), or null
   int* progress;                   // highest pair tile (tagged with the epoch) this rank's GEMM has started
   int push_lead;                   // raster groups the pushers may run ahead of the GEMM (0 = unlimited)
@@ -333,10 +332,7 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
       fence_proxy_async_all();
       if (!w.dead) {
         int* ctr = reinterpret_cast<int*>(P.peer_counters[d]) + mi;
-        if (P.push_flags & 1)
-          red_relaxed_sys_add(ctr, 1);
-        else
-          red_release_sys_add(ctr, 1);
+        red_release_sys_add(ctr, 1);
       }
     }
     w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
@@ -489,10 +485,7 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
       fence_proxy_async_all();
       if (!w.dead) {
         int* ctr = reinterpret_cast<int*>(P.peer_counters[d]) + mi;
-        if (P.push_flags & 1)
-          red_relaxed_sys_add(ctr, 1);
-        else
-          red_release_sys_add(ctr, 1);
+        red_release_sys_add(ctr, 1);
       }
     }
     w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;

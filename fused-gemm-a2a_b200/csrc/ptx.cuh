@@ -235,9 +235,6 @@ __device__ __forceinline__ void tmem_ld_wait() {
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void red_relaxed_sys_add(int* p, int v) {
-  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
