@@ -16,6 +16,10 @@ done by libfga.so through its C ABI: symmetric buffers are cudaMalloc'ed once pe
 mapped into every peer with CUDA IPC handles exchanged once over the CP group; the GEMMs are
 hand-written TMA/tcgen05 kernels whose epilogue (push) or pusher warps (receive) perform the
 all-to-all over NVLink. No kernel is compiled at run time and nothing falls back to the CPU.
+
+Layout of this file: memory (slabs of symmetric memory and their peer tables), the per-group
+runtime `_Comm` (barrier, status word, GEMM launches), gradient helpers, the two autograd
+functions, the buffer sets and their active-length views, and the public classes.
 """
 import os
 from dataclasses import dataclass, field
@@ -43,9 +47,25 @@ WGRAD_BACKEND = os.environ.get('FUSED_WGRAD_BACKEND', 'torch')
 if WGRAD_BACKEND not in ('torch', 'fused_accum'):
     raise ValueError('FUSED_WGRAD_BACKEND must be torch or fused_accum')
 
-_ALIGN = 1024  # every sub-buffer of a symmetric slab starts on a 1 KiB boundary
+_ALIGN = 1024        # every region of a slab starts on a 1 KiB boundary
+_HANDLE_BYTES = 64   # size of an exported memory handle (FGA_IPC_HANDLE_BYTES)
+_ROW_TILE = MMA_TILER_MN[0]   # rows of a CTA pair: capacities are multiples of it
 
 
+def _itemsize(dtype):
+    return torch.empty(0, dtype=dtype).element_size()
+
+
+def _numel(shape):
+    total = 1
+    for extent in shape:
+        total *= extent
+    return total
+
+
+# ----------------------------------------------------------------------------------------------
+# Symmetric memory
+# ----------------------------------------------------------------------------------------------
 class _DevicePointer:
     """Exposes raw device memory to torch through the CUDA array interface."""
 
@@ -61,29 +81,42 @@ def _wrap(address, nbytes, device):
 def slab_offsets(layout):
     """Byte (offset, size) of every (name, shape, dtype) entry of a slab and the slab's total size;
     each entry starts on a 1 KiB boundary."""
-    offsets, total = [], 0
+    placed, cursor = [], 0
     for _, shape, dtype in layout:
-        count = 1
-        for extent in shape:
-            count *= extent
-        nbytes = count * torch.empty(0, dtype=dtype).element_size()
-        offsets.append((total, nbytes))
-        total += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
-    return offsets, total
+        size = _numel(shape) * _itemsize(dtype)
+        placed.append((cursor, size))
+        cursor += -(-size // _ALIGN) * _ALIGN
+    return placed, cursor
 
 
 def exchange_handles(group, rank, peers, handle, local_address, open_peer):
     """All-gather one 64-byte memory handle per rank over the CP group (the only collective of a
     buffer's lifetime) and map every peer's allocation: returns the P addresses under which this
     rank reaches each rank's buffer, its own through `local_address`."""
-    gathered = [None] * peers
-    dist.all_gather_object(gathered, (rank, bytes(handle)), group=group)
-    addresses = []
-    for peer, (sender, raw) in enumerate(gathered):
-        if sender != peer or len(raw) != 64:
+    inbox = [None] * peers
+    dist.all_gather_object(inbox, (rank, bytes(handle)), group=group)
+    reachable = []
+    for owner, entry in enumerate(inbox):
+        sender, raw = entry
+        if sender != owner or len(raw) != _HANDLE_BYTES:
             raise RuntimeError('Memory handle exchange returned a malformed entry')
-        addresses.append(local_address if peer == rank else open_peer(raw))
-    return addresses
+        reachable.append(local_address if owner == rank else open_peer(raw))
+    return reachable
+
+
+class _Slab:
+    """One symmetric allocation: the local bytes and the address of the same allocation on every
+    rank as seen from this one. Regions of it become tensors with their int64 peer tables."""
+
+    def __init__(self, base, nbytes, peer_bases, device):
+        self.base, self.nbytes, self.peer_bases, self.device = base, nbytes, peer_bases, device
+        self.bytes = _wrap(base, nbytes, device)
+
+    def region(self, offset, shape, dtype):
+        size = _numel(shape) * _itemsize(dtype)
+        tensor = self.bytes[offset:offset + size].view(dtype).view(shape)
+        table = torch.tensor([peer + offset for peer in self.peer_bases], dtype=torch.int64, device=self.device)
+        return tensor, table
 
 
 class _RecvBuffer:
@@ -91,10 +124,13 @@ class _RecvBuffer:
     rows), both with their peer address tables, and the device-side invocation counter."""
 
     def __init__(self, recv, peer_recv, counters, peer_counters, epoch):
-        self.recv, self.peer_recv = recv, peer_recv
-        self.counters, self.peer_counters, self.epoch = counters, peer_counters, epoch
+        self.recv, self.counters, self.epoch = recv, counters, epoch
+        self.peer_recv, self.peer_counters = peer_recv, peer_counters
 
 
+# ----------------------------------------------------------------------------------------------
+# Per-group runtime
+# ----------------------------------------------------------------------------------------------
 class _Comm:
     """Per (process group, device) state: rank, barrier flags, the device status word and the pool
     of symmetric allocations. Layers of equal geometry share buffers, so the footprint does not
@@ -104,94 +140,97 @@ class _Comm:
 
     @classmethod
     def get(cls, group):
-        key = (group, torch.cuda.current_device())
-        if key not in cls._instances:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError('Create FusedGemmA2AWorkspace before capture to initialize communication')
-            cls._instances[key] = cls(group)
-        return cls._instances[key]
+        slot = (group, torch.cuda.current_device())
+        existing = cls._instances.get(slot)
+        if existing is not None:
+            return existing
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError('Create FusedGemmA2AWorkspace before capture to initialize communication')
+        created = cls._instances[slot] = cls(group)
+        return created
 
     def __init__(self, group):
-        self.group = dist.group.WORLD if group is None else group
-        self.rank, self.p = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.group = group if group is not None else dist.group.WORLD
+        self.p = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
         validate_peer_count(self.p)
         if torch.cuda.get_device_capability()[0] != 10:
             raise ValueError('These kernels target SM100/Blackwell GPUs')
         _native.lib()  # fail here, loudly, if the CUDA library was never built
         self.device = torch.device('cuda', torch.cuda.current_device())
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.progress = torch.zeros(1, dtype=torch.int32, device=self.device)  # GEMM progress for pusher pacing
-        self.compiled = {}   # launch plans by geometry (nothing is compiled; kept for introspection)
+        self.status = self._words(4)      # {code, where, detail, 0} of the first bounded wait that expired
+        self.progress = self._words(1)    # row tile the recv GEMM has reached (pusher pacing)
+        self.compiled = {}                # launch plans by geometry (nothing is compiled; kept for introspection)
         self.pool = {}
         self.projection_buffers = {}
         self._allocations = []
         self.flags, self.peer_flags = self.symmetric((self.p,), torch.int64)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.epoch = self._words(1)
         torch.cuda.synchronize()
         dist.barrier(self.group)
+
+    def _words(self, count):
+        return torch.zeros(count, dtype=torch.int32, device=self.device)
 
     # -- symmetric memory ------------------------------------------------------------------
     def symmetric_bytes(self, nbytes):
         """Allocate `nbytes` of zeroed device memory, map it into every peer and return
         (local address, list of P addresses of the same buffer as seen from this rank)."""
-        lib = _native.lib()
-        base = _native.c_void_p()
-        _native.check(lib.fga_symm_alloc(nbytes, _native.ctypes.byref(base)))
-        self._allocations.append(base.value)
-        addresses = [base.value] * self.p
-        if self.p > 1:
-            handle = _native.ctypes.create_string_buffer(64)
-            _native.check(lib.fga_symm_export(base, handle))
+        lib, ct = _native.lib(), _native.ctypes
+        local = _native.c_void_p()
+        _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
+        self._allocations.append(local.value)
+        if self.p == 1:
+            seen = [local.value]
+        else:
+            handle = ct.create_string_buffer(_HANDLE_BYTES)
+            _native.check(lib.fga_symm_export(local, handle))
 
             def open_peer(raw):
-                mapped = _native.c_void_p()
-                _native.check(lib.fga_symm_open(raw, _native.ctypes.byref(mapped)))
-                return mapped.value
+                remote = _native.c_void_p()
+                _native.check(lib.fga_symm_open(raw, ct.byref(remote)))
+                return remote.value
 
-            addresses = exchange_handles(self.group, self.rank, self.p, handle.raw, base.value, open_peer)
-        valid = torch.tensor(int(all(a and a % 16 == 0 for a in addresses)), device=self.device)
+            seen = exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer)
+        usable = torch.tensor(int(all(address and address % 16 == 0 for address in seen)), device=self.device)
         if self.p > 1:
-            dist.all_reduce(valid, op=dist.ReduceOp.MIN, group=self.group)
-        if not valid.item():
+            dist.all_reduce(usable, op=dist.ReduceOp.MIN, group=self.group)
+        if not usable.item():
             raise RuntimeError('Peer buffers must be aligned and GPU-addressable')
-        return base.value, addresses
+        return local.value, seen
+
+    def _allocate(self, nbytes):
+        base, peer_bases = self.symmetric_bytes(nbytes)
+        return _Slab(base, nbytes, peer_bases, self.device)
 
     def symmetric(self, shape, dtype):
         """A zeroed symmetric tensor and the int64 device table of its address on every peer."""
-        count = 1
-        for extent in shape:
-            count *= extent
-        nbytes = max(16, count * torch.empty(0, dtype=dtype).element_size())
-        base, addresses = self.symmetric_bytes(nbytes)
-        tensor = _wrap(base, nbytes, self.device)[:count * torch.empty(0, dtype=dtype).element_size()]
-        tensor = tensor.view(dtype).view(shape)
-        return tensor, torch.tensor(addresses, dtype=torch.int64, device=self.device)
+        nbytes = max(16, _numel(shape) * _itemsize(dtype))
+        return self._allocate(nbytes).region(0, shape, dtype)
 
     def slab(self, layout):
         """One symmetric allocation carved into named sub-buffers. layout: [(name, shape, dtype)].
         Returns {name: (tensor, peer address table)}; a single handle exchange serves them all."""
-        offsets, total = slab_offsets(layout)
-        base, addresses = self.symmetric_bytes(total)
-        whole = _wrap(base, total, self.device)
-        views = {}
-        for (name, shape, dtype), (offset, nbytes) in zip(layout, offsets):
-            tensor = whole[offset:offset + nbytes].view(dtype).view(shape)
-            table = torch.tensor([a + offset for a in addresses], dtype=torch.int64, device=self.device)
-            views[name] = (tensor, table)
-        return views
+        placed, total = slab_offsets(layout)
+        memory = self._allocate(total)
+        return {name: memory.region(offset, shape, dtype)
+                for (name, shape, dtype), (offset, _) in zip(layout, placed)}
 
     def pooled(self, key, shape, dtype):
-        k = (key, tuple(shape), dtype)
-        if k not in self.pool:
-            self.pool[k] = self.symmetric(shape, dtype)
-        return self.pool[k]
+        slot = (key, tuple(shape), dtype)
+        if slot not in self.pool:
+            self.pool[slot] = self.symmetric(shape, dtype)
+        return self.pool[slot]
 
     # -- synchronization -------------------------------------------------------------------
     def barrier(self, bump=False, epoch=None, counters=None):
         """Device-side group barrier on the current stream. bump=True first zeroes `counters` and
         afterwards advances `epoch` (a receive buffer's invocation counter)."""
+        advanced = None
+        if bump:
+            advanced = self.epoch if epoch is None else epoch
         device_barrier(self.flags, self.peer_flags, self.rank, self.p, self.status, bump=bump,
-                       counters=counters, epoch=(self.epoch if epoch is None else epoch) if bump else None)
+                       counters=counters, epoch=advanced)
 
     def check_status(self):
         """Synchronize and raise if any kernel of this group gave up on a bounded wait."""
@@ -226,46 +265,58 @@ class _Comm:
             raise NotImplementedError('The block-scaled MXFP8 GEMM is not part of this build yet')
         if mode not in ('push', 'recv'):
             raise ValueError('GEMM mode must be push/recv and tile N must divide output width')
-        if not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+        if not all(t.is_contiguous() for t in (a, b, c)):
             raise ValueError('Fused kernels need contiguous tensors')
-        a_rows = a.shape[0] if a_rows is None else a_rows
-        src_rows = a.shape[0] if src_rows is None else src_rows
-        if src_rows < 1 or src_rows > a.shape[0]:
+        rows, depth = a.shape
+        padded = rows if a_rows is None else a_rows
+        logical = rows if src_rows is None else src_rows
+        if not 1 <= logical <= rows:
             raise ValueError('Receive source rows must be positive and fit the receive buffer')
-        if a_rows < a.shape[0] or a_rows % MMA_TILER_MN[0] or (mode == 'recv' and a_rows != a.shape[0]):
+        if padded < rows or padded % _ROW_TILE or (mode == 'recv' and padded != rows):
             raise ValueError('a_rows must be a tile multiple >= the rows of a, and equal to them in recv mode')
-        output_width = b.shape[1] if b_is_kn else b.shape[0]
-        if mode == 'recv':  # the kernel narrows its output tile when 256 does not divide the width
-            tile_n = MMA_N_RECV if output_width % MMA_N_RECV == 0 else MMA_N
-        else:
-            tile_n = MMA_N_OUT_PUSH if num_segments == 1 else MMA_N
-        validate_tile_n(mode, tile_n, output_width, self.p, n_segment,
-                        num_segments if mode == 'push' else num_in, head_dim)
-        if bias is not None and (mode != 'push' or tuple(bias.shape) != (output_width,)
-                                 or bias.dtype != torch.bfloat16):
-            raise ValueError('GEMM bias requires push mode and a BF16 vector of output-width entries')
-        if any(len(x) != self.p for x in aux) or (mode == 'recv' and counters.numel() != c.shape[0] // CTA_M):
-            raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
-        key = (mode, tuple(a.shape), a_rows, tuple(b.shape), b_is_kn, tuple(c.shape), num_in, n_segment,
-               num_segments, bias is not None, src_rows != a.shape[0])
-        self.compiled.setdefault(key, len(self.compiled))
-        lib, stream = _native.lib(), torch.cuda.current_stream().cuda_stream
+        width = b.shape[1] if b_is_kn else b.shape[0]
         if mode == 'push':
-            tables = _native.ptr_array([t.data_ptr() for t in aux[:num_segments]])
-            _native.check(lib.fga_gemm_push(
-                a.data_ptr(), a.shape[0], a.shape[1], a_rows, b.data_ptr(), int(b_is_kn),
-                0 if bias is None else bias.data_ptr(), num_segments, n_segment, tables,
-                c.shape[0] // self.p, self.rank, self.p, self.status.data_ptr(),
-                _k.DEVICE_TIMEOUT_NS, stream))
+            tile_n = MMA_N if num_segments > 1 else MMA_N_OUT_PUSH
+            routed = num_segments
+        else:  # the kernel narrows its output tile when 256 does not divide the width
+            tile_n = MMA_N if width % MMA_N_RECV else MMA_N_RECV
+            routed = num_in
+        validate_tile_n(mode, tile_n, width, self.p, n_segment, routed, head_dim)
+        if bias is not None and not (mode == 'push' and tuple(bias.shape) == (width,) and bias.dtype == torch.bfloat16):
+            raise ValueError('GEMM bias requires push mode and a BF16 vector of output-width entries')
+        tables_ok = all(len(table) == self.p for table in aux)
+        if not tables_ok or (mode == 'recv' and counters.numel() != c.shape[0] // CTA_M):
+            raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
+        plan = (mode, tuple(a.shape), padded, tuple(b.shape), b_is_kn, tuple(c.shape), num_in, n_segment,
+                num_segments, bias is not None, logical != rows)
+        self.compiled.setdefault(plan, len(self.compiled))
+        if mode == 'push':
+            self._launch_push(a, padded, b, b_is_kn, bias, aux[:num_segments], n_segment, c.shape[0] // self.p)
         else:
-            split = self.push_split(a, num_in, self.p)
-            sources = _native.ptr_array([int(s) for s in list(srcs)[:num_in]])
-            _native.check(lib.fga_gemm_recv(
-                a.data_ptr(), a.shape[0], a.shape[1], b.data_ptr(), int(b_is_kn), output_width,
-                c.data_ptr(), aux[0].data_ptr(), aux[1].data_ptr(), counters.data_ptr(), sources,
-                num_in, src_rows, split, self.rank, self.p, roles,
-                self.flags.data_ptr() + 8 * self.rank, self.progress.data_ptr(), self.status.data_ptr(),
-                _k.DEVICE_TIMEOUT_NS, stream))
+            self._launch_recv(a, b, b_is_kn, width, c, aux, counters, list(srcs)[:num_in], logical, roles)
+
+    def _launch_push(self, a, a_rows, b, b_is_kn, bias, peer_tables, n_segment, head_rows):
+        tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
+        _native.check(_native.lib().fga_gemm_push(
+            a.data_ptr(), a.shape[0], a.shape[1], a_rows, b.data_ptr(), int(b_is_kn),
+            bias.data_ptr() if bias is not None else 0, len(peer_tables), n_segment, tables, head_rows,
+            self.rank, self.p, self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS,
+            torch.cuda.current_stream().cuda_stream))
+
+    def _launch_recv(self, recv, b, b_is_kn, width, c, aux, counters, srcs, src_rows, roles):
+        peer_recv, peer_counters = aux
+        sources = _native.ptr_array([int(address) for address in srcs])
+        _native.check(_native.lib().fga_gemm_recv(
+            recv.data_ptr(), recv.shape[0], recv.shape[1], b.data_ptr(), int(b_is_kn), width, c.data_ptr(),
+            peer_recv.data_ptr(), peer_counters.data_ptr(), counters.data_ptr(), sources, len(srcs),
+            src_rows, self.push_split(recv, len(srcs), self.p), self.rank, self.p, roles,
+            self._pacing_epoch(), self.progress.data_ptr(), self.status.data_ptr(),
+            _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+
+    def _pacing_epoch(self):
+        """Address of this rank's own barrier flag: a device word that grows with every barrier,
+        which the recv kernel uses to tag its progress word (no clearing between invocations)."""
+        return self.flags.data_ptr() + 8 * self.rank
 
     def recv_gemm(self, a, b, b_is_kn, c, peer_recv, peer_counters, counters, num_in, srcs,
                   head_dim=0, src_rows=None):
@@ -274,9 +325,13 @@ class _Comm:
                   srcs=srcs, head_dim=head_dim, src_rows=src_rows)
 
 
+# ----------------------------------------------------------------------------------------------
+# Gradients of the parameters
+# ----------------------------------------------------------------------------------------------
 def _check(t, shape, label):
-    if tuple(t.shape) != tuple(shape) or t.dtype != torch.bfloat16 or not t.is_contiguous():
-        raise ValueError(f'{label} must be a contiguous BF16 tensor of shape {tuple(shape)}, got {tuple(t.shape)}')
+    shape = tuple(shape)
+    if tuple(t.shape) != shape or t.dtype != torch.bfloat16 or not t.is_contiguous():
+        raise ValueError(f'{label} must be a contiguous BF16 tensor of shape {shape}, got {tuple(t.shape)}')
 
 
 _placeholder_grads = {}
@@ -287,13 +342,21 @@ def _accumulated(param):
     shape-cached placeholder (zeroed on request) so gradient-ready hooks still fire
     (reference fused_gemm_a2a.py:281-294)."""
     param.grad_added_to_main_grad = True
-    key = (param.device, param.dtype, tuple(param.shape))
-    dummy = _placeholder_grads.get(key)
-    if dummy is None:
-        dummy = _placeholder_grads[key] = torch.empty(param.shape, device=param.device, dtype=param.dtype)
+    slot = (param.device, param.dtype, tuple(param.shape))
+    if slot not in _placeholder_grads:
+        _placeholder_grads[slot] = torch.empty(param.shape, device=param.device, dtype=param.dtype)
+    placeholder = _placeholder_grads[slot]
     if getattr(param, 'zero_out_wgrad', False):
-        dummy.zero_()
-    return dummy.detach()
+        placeholder.zero_()
+    return placeholder.detach()
+
+
+def _usable_main_grad(main_grad, weight, *, same_device):
+    """The accumulating epilogue writes FP32 rows of the weight's shape through 16-byte bulk
+    reductions: anything else would be silently truncated or misaligned."""
+    return (main_grad.shape == weight.shape and main_grad.dtype == torch.float32
+            and main_grad.is_contiguous() and main_grad.data_ptr() % 16 == 0
+            and (not same_device or main_grad.device == weight.device))
 
 
 def _weight_grad(weight, a, b, precision='bf16', status=None):
@@ -301,23 +364,22 @@ def _weight_grad(weight, a, b, precision='bf16', status=None):
     epilogue accumulates straight into it; otherwise a BF16 gradient is returned
     (reference fused_gemm_a2a.py:249-275)."""
     main_grad = getattr(weight, 'main_grad', None)
+    into_main_grad = main_grad is not None
     if precision == 'mxfp8':
-        if main_grad is not None and (
-                main_grad.shape != weight.shape or main_grad.device != weight.device
-                or main_grad.dtype != torch.float32 or not main_grad.is_contiguous()
-                or main_grad.data_ptr() % 16):
+        if into_main_grad and not _usable_main_grad(main_grad, weight, same_device=True):
             raise ValueError('MXFP8 main_grad must match the weight shape and device, '
                              'with contiguous FP32 storage and 16-byte alignment')
-        out = torch.empty_like(weight) if main_grad is None else main_grad
-        mxfp8_wgrad(a, b, out, accumulate=main_grad is not None)
-        return out if main_grad is None else _accumulated(weight)
+        target = main_grad if into_main_grad else torch.empty_like(weight)
+        mxfp8_wgrad(a, b, target, accumulate=into_main_grad)
+        return _accumulated(weight) if into_main_grad else target
     if status is None:
-        status = _Comm.get(None).status if dist.is_initialized() else torch.zeros(
-            4, dtype=torch.int32, device=a.device)
-    if main_grad is None:
+        if dist.is_initialized():
+            status = _Comm.get(None).status
+        else:
+            status = torch.zeros(4, dtype=torch.int32, device=a.device)
+    if not into_main_grad:
         return bf16_wgrad(a, b, torch.empty(weight.shape, device=a.device, dtype=a.dtype), status)
-    if (main_grad.shape != weight.shape or main_grad.dtype != torch.float32
-            or not main_grad.is_contiguous() or main_grad.data_ptr() % 16):
+    if not _usable_main_grad(main_grad, weight, same_device=False):
         raise ValueError('main_grad must match the weight shape with contiguous, 16-byte aligned FP32 storage')
     bf16_wgrad(a, b, main_grad, status, accumulate=True)
     return _accumulated(weight)
@@ -328,11 +390,19 @@ def _bias_grad(bias, dy_rows, accumulate=True, *, use_cute=False):
     accumulate is set, else returned in the parameter dtype (reference fused_gemm_a2a.py:297-309)."""
     if bias is None:
         return None
-    main_grad = getattr(bias, 'main_grad', None)
-    if main_grad is None or not accumulate:
-        return reduce_bias_grad(dy_rows, torch.empty_like(bias))
-    reduce_bias_grad(dy_rows, main_grad, accumulate=True)
-    return _accumulated(bias)
+    main_grad = getattr(bias, 'main_grad', None) if accumulate else None
+    if main_grad is not None:
+        reduce_bias_grad(dy_rows, main_grad, accumulate=True)
+        return _accumulated(bias)
+    return reduce_bias_grad(dy_rows, torch.empty_like(bias))
+
+
+# ----------------------------------------------------------------------------------------------
+# Autograd
+# ----------------------------------------------------------------------------------------------
+def _as_heads(matrix, head_dim):
+    """[rows, heads*D] -> [rows, heads, D] without copying."""
+    return matrix.view(-1, matrix.shape[1] // head_dim, head_dim)
 
 
 class _FusedQKV(torch.autograd.Function):
@@ -341,34 +411,35 @@ class _FusedQKV(torch.autograd.Function):
     @staticmethod
     @record_function('fused_qkv_forward')
     def forward(ctx, x, weight, bias, module, workspace):
-        comm, tokens = workspace.comm, x.shape[0]
-        comm.barrier()                      # every rank is done reading the head-side buffers
-        workspace.run_push(x, weight, False, module.segments,
-                           bias=bias if module.bias_in_gemm else None)
-        comm.barrier()                      # every incoming tile has landed
-        ctx.module, ctx.workspace, ctx.tokens = module, workspace, tokens
-        ctx.has_bias = bias is not None
-        ctx.save_for_backward(*((x, weight) if bias is None else (x, weight, bias)))
+        comm = workspace.comm
+        early_bias = bias if module.bias_in_gemm else None
         late_bias = bias if (module.apply_bias and not module.bias_in_gemm) else None
-        owned = resize_rank_rows(workspace.heads, comm.p, tokens, copy=True, bias=late_bias,
+        comm.barrier()                      # every rank is done reading the head-side buffers
+        workspace.run_push(x, weight, False, module.segments, bias=early_bias)
+        comm.barrier()                      # every incoming tile has landed
+        ctx.module, ctx.workspace, ctx.tokens, ctx.has_bias = module, workspace, x.shape[0], bias is not None
+        ctx.save_for_backward(x, weight, *(() if bias is None else (bias,)))
+        # One pass strips the tile padding, applies a late bias and gives the caller storage of its
+        # own: the shared buffers are overwritten by the next call of this geometry.
+        owned = resize_rank_rows(workspace.heads, comm.p, x.shape[0], copy=True, bias=late_bias,
                                  head_dim=module.head_dim,
                                  head_offset=comm.rank * module.num_heads // comm.p)
-        return tuple(t.view(-1, t.shape[1] // module.head_dim, module.head_dim) for t in owned)
+        return tuple(_as_heads(t, module.head_dim) for t in owned)
 
     @staticmethod
     @record_function('fused_qkv_backward')
     def backward(ctx, *head_grads):
-        saved = ctx.saved_tensors
-        x, weight = saved[0], saved[1]
+        x, weight = ctx.saved_tensors[:2]
         workspace, tokens, module = ctx.workspace, ctx.tokens, ctx.module
-        sources = [g.contiguous().flatten(1) for g in head_grads]
         workspace.begin_recv()
         dx = torch.empty(workspace.capacity, x.shape[1], device=x.device, dtype=x.dtype)
-        workspace.run_recv(sources, weight, True, dx)
+        workspace.run_recv([g.contiguous().flatten(1) for g in head_grads], weight, True, dx)
         # The receive buffer now holds this rank's dY in weight-row order; pad rows are not read.
+        # Saved-tensor hooks may hand back a plain tensor for the weight, so main_grad and the
+        # other parameter metadata are taken from the module's own Parameter.
         dy = workspace.recv[:tokens]
         dw = _weight_grad(module.weight, dy, x, workspace.precision, workspace.comm.status)
-        db = _bias_grad(module.bias if ctx.has_bias else None, dy, module.accumulate_bias_grad)
+        db = _bias_grad(module.bias, dy, module.accumulate_bias_grad) if ctx.has_bias else None
         return dx[:tokens], dw, db, None, None
 
 
@@ -381,13 +452,12 @@ class _FusedOutput(torch.autograd.Function):
         workspace.begin_recv()
         y = torch.empty(workspace.capacity, weight.shape[0], device=o.device, dtype=o.dtype)
         workspace.run_recv([o.flatten(1)], weight, False, y)
-        ctx.module, ctx.workspace, ctx.tokens = module, workspace, tokens
-        ctx.has_bias = bias is not None
+        ctx.module, ctx.workspace, ctx.tokens, ctx.has_bias = module, workspace, tokens, bias is not None
         # The sequence-side O lives in the shared receive buffer, which the next call of this
         # geometry overwrites; backward needs it for dW, so keep a private copy of the logical rows.
         ctx.save_for_backward(weight, workspace.recv[:tokens].clone())
         y = y[:tokens]
-        if bias is not None and module.apply_bias:
+        if module.apply_bias and bias is not None:
             y.add_(bias.view(1, -1))
         return y
 
@@ -407,9 +477,12 @@ class _FusedOutput(torch.autograd.Function):
         db = _bias_grad(module.bias, dy, module.accumulate_bias_grad) if ctx.has_bias else None
         comm.barrier()
         do, = resize_rank_rows(workspace.heads, comm.p, tokens, copy=True)
-        return do.view(-1, do.shape[1] // module.head_dim, module.head_dim), dw, db, None, None, None
+        return _as_heads(do, module.head_dim), dw, db, None, None, None
 
 
+# ----------------------------------------------------------------------------------------------
+# Buffer sets and their active-length views
+# ----------------------------------------------------------------------------------------------
 class _ProjectionBuffers:
     """Maximum-capacity buffers of one (capacity, hidden, head_dim, segments) geometry: `segments`
     head-side buffers [P*capacity, H/P], a receive buffer [capacity, segments*H] and its counters,
@@ -417,26 +490,29 @@ class _ProjectionBuffers:
 
     def __init__(self, comm, capacity, hidden_size, head_dim, segments):
         self.comm, self.capacity, self.head_dim = comm, capacity, head_dim
-        self.workspaces = {}
+        self.workspaces = {}              # active-length views by (capacity, precision)
         self.mx_recv = self.mx_scale = None
-        layout = [(f'head{i}', (comm.p * capacity, hidden_size // comm.p), torch.bfloat16)
-                  for i in range(segments)]
-        layout += [('recv', (capacity, segments * hidden_size), torch.bfloat16),
-                   ('counters', (capacity // CTA_M,), torch.int32)]
-        views = comm.slab(layout)
-        self.heads = [views[f'head{i}'][0] for i in range(segments)]
-        self.peer_heads = [views[f'head{i}'][1] for i in range(segments)]
-        self.recv, self.peer_recv = views['recv']
-        self.counters, self.peer_counters = views['counters']
+        head_names = [f'head{index}' for index in range(segments)]
+        head_shape = (comm.p * capacity, hidden_size // comm.p)
+        regions = comm.slab([(name, head_shape, torch.bfloat16) for name in head_names] + [
+            ('recv', (capacity, segments * hidden_size), torch.bfloat16),
+            ('counters', (capacity // CTA_M,), torch.int32)])
+        self.heads, self.peer_heads = map(list, zip(*(regions[name] for name in head_names)))
+        self.recv, self.peer_recv = regions['recv']
+        self.counters, self.peer_counters = regions['counters']
         self.epoch = torch.zeros(1, dtype=torch.int32, device=comm.device)
         torch.cuda.synchronize()
         dist.barrier(comm.group)
 
     def init_mxfp8(self):
-        if self.mx_recv is None:
-            rows, k = self.recv.shape
-            self.mx_recv = torch.empty((rows, k), device=self.recv.device, dtype=torch.float8_e4m3fn)
-            self.mx_scale = torch.empty((rows * k // 32,), device=self.recv.device, dtype=torch.uint8)
+        """Local (not symmetric) E4M3 copy of the receive buffer and its scale bytes: only BF16
+        crosses the links, the quantized operand is produced where it is consumed."""
+        if self.mx_recv is not None:
+            return
+        rows, k = self.recv.shape
+        device = self.recv.device
+        self.mx_recv = torch.empty((rows, k), device=device, dtype=torch.float8_e4m3fn)
+        self.mx_scale = torch.empty((rows * k // 32,), device=device, dtype=torch.uint8)
 
 
 class _ProjectionWorkspace:
@@ -445,65 +521,85 @@ class _ProjectionWorkspace:
 
     def __init__(self, buffers, capacity, precision):
         comm = buffers.comm
-        self.comm, self.capacity, self.head_dim, self.precision = comm, capacity, buffers.head_dim, precision
-        self.heads = [buf[:comm.p * capacity] for buf in buffers.heads]
-        self.peer_heads = buffers.peer_heads
-        self.recv, self.peer_recv = buffers.recv[:capacity], buffers.peer_recv
-        self.counters, self.peer_counters = buffers.counters[:capacity // CTA_M], buffers.peer_counters
-        self.epoch = buffers.epoch
+        self.comm, self.capacity, self.precision = comm, capacity, precision
+        self.head_dim, self.epoch = buffers.head_dim, buffers.epoch
+        blocks = capacity // CTA_M
+        self.heads = [head[:comm.p * capacity] for head in buffers.heads]
+        self.recv, self.counters = buffers.recv[:capacity], buffers.counters[:blocks]
+        self.peer_heads, self.peer_recv, self.peer_counters = (
+            buffers.peer_heads, buffers.peer_recv, buffers.peer_counters)
         if precision == 'mxfp8':
             self.mx_recv = buffers.mx_recv[:capacity]
             self.mx_scale = buffers.mx_scale[:capacity * self.recv.shape[1] // 32]
 
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
     def run_push(self, a, weight, b_is_kn, segments, bias=None):
+        comm = self.comm
         width = weight.shape[1] if b_is_kn else weight.shape[0]
-        if self.precision == 'mxfp8':
-            # Both operands are requantized from BF16 on every call, each along this GEMM's
-            # reduction axis (reference fused_gemm_a2a.py:439-448).
-            aq, sa = mxfp8_quantize(a)
-            wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
-            comm = self.comm
-            validate_tile_n('push', MMA_N_OUT_PUSH if segments == 1 else MMA_N, width, comm.p,
-                            width // segments, segments, self.head_dim)
-            tables = _native.ptr_array([t.data_ptr() for t in self.peer_heads[:segments]])
-            _native.check(_native.lib().fga_gemm_push_mx(
-                aq.data_ptr(), sa.data_ptr(), aq.shape[0], aq.shape[1], self.capacity, wq.data_ptr(),
-                sb.data_ptr(), wq.shape[0], 0 if bias is None else bias.data_ptr(), segments,
-                width // segments, tables, self.capacity, comm.rank, comm.p, comm.status.data_ptr(),
-                _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+        n_segment = width // segments
+        if self.precision != 'mxfp8':
+            comm.gemm('push', a, weight, b_is_kn, self.heads[0], self.peer_heads, self.counters, 0,
+                      n_segment, segments, a_rows=self.capacity, head_dim=self.head_dim, bias=bias)
             return
-        self.comm.gemm('push', a, weight, b_is_kn, self.heads[0], self.peer_heads, self.counters, 0,
-                       width // segments, segments, a_rows=self.capacity, head_dim=self.head_dim,
-                       bias=bias)
+        # MXFP8: both operands are requantized from BF16 on every call, each along this GEMM's
+        # reduction axis (reference fused_gemm_a2a.py:439-448).
+        aq, sa = mxfp8_quantize(a)
+        wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+        validate_tile_n('push', MMA_N_OUT_PUSH if segments == 1 else MMA_N, width, comm.p,
+                        n_segment, segments, self.head_dim)
+        tables = _native.ptr_array([table.data_ptr() for table in self.peer_heads[:segments]])
+        _native.check(_native.lib().fga_gemm_push_mx(
+            aq.data_ptr(), sa.data_ptr(), aq.shape[0], aq.shape[1], self.capacity, wq.data_ptr(),
+            sb.data_ptr(), wq.shape[0], bias.data_ptr() if bias is not None else 0, segments, n_segment,
+            tables, self.capacity, comm.rank, comm.p, comm.status.data_ptr(), _k.DEVICE_TIMEOUT_NS,
+            self._stream()))
 
     def begin_recv(self):
         self.comm.barrier(bump=True, epoch=self.epoch, counters=self.counters)
 
     def run_recv(self, inputs, weight, b_is_kn, out, roles=3):
-        shape = inputs[0].shape
-        if any(t.shape != shape for t in inputs):
+        comm = self.comm
+        rows_in = inputs[0].shape[0]
+        if any(t.shape != inputs[0].shape for t in inputs):
             raise ValueError('All head-side inputs must have the same shape')
-        if shape[0] % self.comm.p:
+        if rows_in % comm.p:
             raise ValueError('Head-side rows must divide evenly over CP ranks')
-        if self.precision == 'mxfp8':
-            # Only BF16 crosses the links; quantizer warps inside the kernel convert each arrived
-            # row block into the local E4M3 copy that the GEMM reads (reference fused_gemm_a2a.py:465-470).
-            comm = self.comm
-            wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
-            k = self.recv.shape[1]
-            split = comm.push_split(self.recv, len(inputs), comm.p)
-            sources = _native.ptr_array([t.data_ptr() for t in inputs])
-            _native.check(_native.lib().fga_gemm_recv_mx(
-                self.recv.data_ptr(), self.mx_recv.data_ptr(), self.mx_scale.data_ptr(), self.capacity, k,
-                wq.data_ptr(), sb.data_ptr(), wq.shape[0], wq.shape[1], out.shape[1], out.data_ptr(),
-                self.peer_recv.data_ptr(), self.peer_counters.data_ptr(), self.counters.data_ptr(), sources,
-                len(inputs), shape[0] // comm.p, split, comm.rank, comm.p, roles,
-                comm.flags.data_ptr() + 8 * comm.rank, comm.progress.data_ptr(), comm.status.data_ptr(),
-                _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+        src_rows = rows_in // comm.p
+        if self.precision != 'mxfp8':
+            comm.gemm('recv', self.recv, weight, b_is_kn, out, [self.peer_recv, self.peer_counters],
+                      self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
+                      head_dim=self.head_dim, src_rows=src_rows, roles=roles)
             return
-        self.comm.gemm('recv', self.recv, weight, b_is_kn, out, [self.peer_recv, self.peer_counters],
-                       self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
-                       head_dim=self.head_dim, src_rows=shape[0] // self.comm.p, roles=roles)
+        # MXFP8: only BF16 crosses the links; quantizer warps inside the kernel convert each arrived
+        # row block into the local E4M3 copy that the GEMM reads (reference fused_gemm_a2a.py:465-470).
+        wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+        sources = _native.ptr_array([t.data_ptr() for t in inputs])
+        _native.check(_native.lib().fga_gemm_recv_mx(
+            self.recv.data_ptr(), self.mx_recv.data_ptr(), self.mx_scale.data_ptr(), self.capacity,
+            self.recv.shape[1], wq.data_ptr(), sb.data_ptr(), wq.shape[0], wq.shape[1], out.shape[1],
+            out.data_ptr(), self.peer_recv.data_ptr(), self.peer_counters.data_ptr(),
+            self.counters.data_ptr(), sources, len(inputs), src_rows,
+            comm.push_split(self.recv, len(inputs), comm.p), comm.rank, comm.p, roles,
+            comm._pacing_epoch(), comm.progress.data_ptr(), comm.status.data_ptr(),
+            _k.DEVICE_TIMEOUT_NS, self._stream()))
+
+
+# ----------------------------------------------------------------------------------------------
+# Public classes
+# ----------------------------------------------------------------------------------------------
+def _head_dim(hidden_size, num_heads):
+    if num_heads <= 0 or hidden_size <= 0 or hidden_size % num_heads:
+        raise ValueError('hidden_size must be positive and divisible by num_heads')
+    return hidden_size // num_heads
+
+
+def _one_tile_per_head(head_dim, tile_n):
+    """The QKV push routes whole heads: one 128-column tile is one (head, q|k|v|gate) unit."""
+    if head_dim != tile_n:
+        raise ValueError(f'QKV needs one N tile per head: set FUSED_MMA_N={head_dim}')
 
 
 @dataclass(frozen=True, eq=False)
@@ -522,62 +618,63 @@ class FusedGemmA2AWorkspace:
     _buffers: dict = field(init=False, repr=False)
 
     def __post_init__(self):
-        if self.precision not in ('bf16', 'mxfp8'):
+        quantized = self.precision == 'mxfp8'
+        if not quantized and self.precision != 'bf16':
             raise ValueError('precision must be bf16 or mxfp8')
-        if self.precision == 'mxfp8' and self.hidden_size != 128 * self.num_heads:
+        if quantized and self.hidden_size != 128 * self.num_heads:
             raise ValueError('Experimental MXFP8 requires head_dim=128')
-        capacity = padded_rows(self.max_local_tokens, MMA_TILER_MN[0])
-        if self.num_heads <= 0 or self.hidden_size <= 0 or self.hidden_size % self.num_heads:
-            raise ValueError('hidden_size must be positive and divisible by num_heads')
+        capacity = padded_rows(self.max_local_tokens, _ROW_TILE)
+        head_dim = _head_dim(self.hidden_size, self.num_heads)
         if not dist.is_initialized():
             raise RuntimeError('Initialize the CP process group before creating FusedGemmA2AWorkspace')
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError('Create FusedGemmA2AWorkspace before CUDA Graph capture')
-        group = dist.group.WORLD if self.cp_group is None else self.cp_group
+        group = self.cp_group if self.cp_group is not None else dist.group.WORLD
         peers = dist.get_world_size(group)
         validate_peer_count(peers)
-        if self.num_heads % peers or (self.hidden_size // peers) % MMA_N or (self.hidden_size // peers) % MMA_N_OUT_PUSH:
+        per_rank_width = self.hidden_size // peers
+        if self.num_heads % peers or per_rank_width % MMA_N or per_rank_width % MMA_N_OUT_PUSH:
             raise ValueError('Heads must split over CP with tile-aligned per-rank width')
-        head_dim = self.hidden_size // self.num_heads
-        if head_dim != MMA_N:
-            raise ValueError(f'QKV needs one N tile per head: set FUSED_MMA_N={head_dim}')
+        _one_tile_per_head(head_dim, MMA_N)
         comm = _Comm.get(group)
-        buffers = {}
-        for segments in (3 + bool(self.gate), 1):
-            key = (capacity, self.hidden_size, head_dim, segments)
-            if key not in comm.projection_buffers:
-                comm.projection_buffers[key] = _ProjectionBuffers(comm, *key)
-            buffers[segments] = comm.projection_buffers[key]
-            if self.precision == 'mxfp8':
-                buffers[segments].init_mxfp8()
-        object.__setattr__(self, 'cp_group', group)
-        object.__setattr__(self, 'comm', comm)
-        object.__setattr__(self, '_buffers', buffers)
+        # One buffer set for the QKV(/gate) side and one for the output side, shared by every
+        # workspace handle and layer of the same geometry on this group.
+        sets = {}
+        for segments in (4 if self.gate else 3, 1):
+            geometry = (capacity, self.hidden_size, head_dim, segments)
+            if geometry not in comm.projection_buffers:
+                comm.projection_buffers[geometry] = _ProjectionBuffers(comm, *geometry)
+            sets[segments] = comm.projection_buffers[geometry]
+            if quantized:
+                sets[segments].init_mxfp8()
+        for name, value in (('cp_group', group), ('comm', comm), ('_buffers', sets)):
+            object.__setattr__(self, name, value)   # the dataclass is frozen for its users
 
     def _validate(self, module, tensor):
-        if self.precision == 'mxfp8' and type(module.weight) not in (torch.Tensor, nn.Parameter):
+        device = self.comm.device
+        weight, bias = module.weight, module.bias
+        if self.precision == 'mxfp8' and type(weight) not in (torch.Tensor, nn.Parameter):
             raise TypeError('MXFP8 currently takes BF16 master weights, not quantized Parameter subclasses')
-        if (module.weight.shape[1] != self.hidden_size or module.num_heads != self.num_heads
-                or module.segments not in self._buffers):
+        same_geometry = (weight.shape[1] == self.hidden_size and module.num_heads == self.num_heads
+                         and module.segments in self._buffers)
+        if not same_geometry:
             raise ValueError('Workspace hidden size, head count and QKV/QKVG mode must match the projection')
-        if module.weight.device != self.comm.device or torch.cuda.current_device() != self.comm.device.index:
+        if weight.device != device or torch.cuda.current_device() != device.index:
             raise ValueError('Workspace and projection must use the current CUDA device')
-        if tensor.device != self.comm.device:
+        if tensor.device != device:
             raise ValueError('Input and workspace must use the same CUDA device')
-        if module.bias is not None and (module.bias.device != self.comm.device or not module.bias.is_contiguous()):
+        if bias is not None and not (bias.device == device and bias.is_contiguous()):
             raise ValueError('Bias must be contiguous and on the workspace CUDA device')
 
     def _view(self, local_tokens, segments):
         """The cached active-length view for `local_tokens`; never allocates device memory."""
         if local_tokens > self.max_local_tokens:
             raise ValueError(f'local_tokens={local_tokens} exceeds max_local_tokens={self.max_local_tokens}')
-        capacity = padded_rows(local_tokens, MMA_TILER_MN[0])
         buffers = self._buffers[segments]
-        key = (capacity, self.precision)
-        view = buffers.workspaces.get(key)
-        if view is None:
-            view = buffers.workspaces[key] = _ProjectionWorkspace(buffers, capacity, self.precision)
-        return view
+        active = (padded_rows(local_tokens, _ROW_TILE), self.precision)
+        if active not in buffers.workspaces:
+            buffers.workspaces[active] = _ProjectionWorkspace(buffers, *active)
+        return buffers.workspaces[active]
 
 
 def _check_workspace(workspace, module, tensor):
@@ -586,7 +683,27 @@ def _check_workspace(workspace, module, tensor):
     workspace._validate(module, tensor)
 
 
-class FusedQKVProjection(nn.Module):
+class _CallerOwnedProjection(nn.Module):
+    """What both projections share: weight and bias are caller-owned tensors kept by reference
+    (never copied, never initialised), checked once at construction."""
+
+    def _adopt(self, hidden_size, num_heads, weight, bias, apply_bias, accumulate_bias_grad):
+        if not isinstance(weight, torch.Tensor):
+            raise TypeError('weight must be a caller-provided tensor')
+        if not (bias is None or isinstance(bias, torch.Tensor)):
+            raise TypeError('bias must be a caller-provided tensor or None')
+        self.head_dim = _head_dim(hidden_size, num_heads)
+        self.num_heads = num_heads
+        self.apply_bias, self.accumulate_bias_grad = apply_bias, accumulate_bias_grad
+
+    def _keep(self, weight, bias, out_rows, hidden_size):
+        _check(weight.data, (out_rows, hidden_size), 'weight')
+        if bias is not None and (tuple(bias.shape) != (out_rows,) or bias.dtype != torch.bfloat16):
+            raise ValueError(f'bias must be a BF16 vector of {out_rows} entries')
+        self.weight, self.bias = weight, bias
+
+
+class FusedQKVProjection(_CallerOwnedProjection):
     """[T/P, H] -> q, k, v [T, heads/P, D] (and gate with gate=True). `weight` is
     [(3 + gate) * H, H] in per-head [q; k; v; gate] row order, `bias` likewise; both are
     caller-owned and kept by reference. apply_bias=False leaves the add to the consumer (dbias is
@@ -599,30 +716,17 @@ class FusedQKVProjection(nn.Module):
     def __init__(self, hidden_size, num_heads, num_kv_heads=None, *, weight, gate=False, bias=None,
                  apply_bias=True, bias_in_gemm=False, accumulate_bias_grad=True):
         super().__init__()
-        if not isinstance(weight, torch.Tensor):
-            raise TypeError('weight must be a caller-provided tensor')
-        if bias is not None and not isinstance(bias, torch.Tensor):
-            raise TypeError('bias must be a caller-provided tensor or None')
         if bias_in_gemm and not apply_bias:
             raise ValueError('bias_in_gemm requires apply_bias=True; the consumer must not add bias again')
-        if num_heads <= 0 or hidden_size <= 0 or hidden_size % num_heads:
-            raise ValueError('hidden_size must be positive and divisible by num_heads')
-        self.apply_bias, self.bias_in_gemm = apply_bias, bias_in_gemm
-        self.accumulate_bias_grad = accumulate_bias_grad
+        self._adopt(hidden_size, num_heads, weight, bias, apply_bias, accumulate_bias_grad)
+        self.bias_in_gemm = bias_in_gemm
         self.segments = 4 if gate else 3
-        self.num_heads = num_heads
-        self.head_dim = hidden_size // num_heads
-        kv_heads = num_kv_heads or num_heads
-        self.n_q, self.n_kv = num_heads * self.head_dim, kv_heads * self.head_dim
+        self.n_q = num_heads * self.head_dim
+        self.n_kv = (num_kv_heads or num_heads) * self.head_dim
         if self.n_kv != self.n_q:
             raise NotImplementedError('GQA is not supported yet; Q, K and V must have equal widths')
-        if self.head_dim != MMA_TILER_MN[1]:
-            raise ValueError(f'QKV needs one N tile per head: set FUSED_MMA_N={self.head_dim}')
-        rows = self.segments * self.n_q
-        _check(weight.data, (rows, hidden_size), 'weight')
-        if bias is not None and (tuple(bias.shape) != (rows,) or bias.dtype != torch.bfloat16):
-            raise ValueError(f'bias must be a BF16 vector of {rows} entries')
-        self.weight, self.bias = weight, bias
+        _one_tile_per_head(self.head_dim, MMA_TILER_MN[1])
+        self._keep(weight, bias, self.segments * self.n_q, hidden_size)
 
     def forward(self, x, workspace):
         _check_workspace(workspace, self, x)
@@ -630,7 +734,7 @@ class FusedQKVProjection(nn.Module):
         return _FusedQKV.apply(x, self.weight, self.bias, self, workspace._view(x.shape[0], self.segments))
 
 
-class FusedOutputProjection(nn.Module):
+class FusedOutputProjection(_CallerOwnedProjection):
     """[T, heads/P, D] -> [T/P, H] with weight [H, H] (reference fused_gemm_a2a.py:610-648).
     apply_bias=False returns y without the bias (the caller fuses it elsewhere) while dbias is
     still produced."""
@@ -638,25 +742,16 @@ class FusedOutputProjection(nn.Module):
     def __init__(self, hidden_size, num_heads, *, weight, bias=None, apply_bias=True,
                  accumulate_bias_grad=True):
         super().__init__()
-        if not isinstance(weight, torch.Tensor):
-            raise TypeError('weight must be a caller-provided tensor')
-        if bias is not None and not isinstance(bias, torch.Tensor):
-            raise TypeError('bias must be a caller-provided tensor or None')
-        if num_heads <= 0 or hidden_size <= 0 or hidden_size % num_heads:
-            raise ValueError('hidden_size must be positive and divisible by num_heads')
-        self.apply_bias, self.accumulate_bias_grad = apply_bias, accumulate_bias_grad
-        self.segments, self.num_heads = 1, num_heads
-        self.head_dim = hidden_size // num_heads
-        _check(weight.data, (hidden_size, hidden_size), 'weight')
-        if bias is not None and (tuple(bias.shape) != (hidden_size,) or bias.dtype != torch.bfloat16):
-            raise ValueError(f'bias must be a BF16 vector of {hidden_size} entries')
-        self.weight, self.bias = weight, bias
+        self._adopt(hidden_size, num_heads, weight, bias, apply_bias, accumulate_bias_grad)
+        self.segments = 1
+        self._keep(weight, bias, hidden_size, hidden_size)
 
     def forward(self, o, workspace):
         _check_workspace(workspace, self, o)
-        hidden, p = self.weight.shape[0], workspace.comm.p
-        _check(o, (o.shape[0], hidden // p // self.head_dim, self.head_dim), 'o')
-        if o.shape[0] % p:
+        peers = workspace.comm.p
+        local_heads = self.weight.shape[0] // peers // self.head_dim
+        _check(o, (o.shape[0], local_heads, self.head_dim), 'o')
+        if o.shape[0] % peers:
             raise ValueError('Token count must be divisible by CP')
-        tokens = o.shape[0] // p
+        tokens = o.shape[0] // peers
         return _FusedOutput.apply(o, self.weight, self.bias, self, workspace._view(tokens, 1), tokens)

@@ -26,45 +26,56 @@ DEVICE_TIMEOUT_NS = int(float(os.environ.get('FGA_TIMEOUT_S', 20)) * 1e9)  # bou
 
 
 # ----------------------------------------------------------------------------- pure geometry
+_BARRIER_LANES = 32          # the device barrier is one warp, one lane per peer
+_JOB_BYTES = 64 * 1024       # target size of one pusher job (rows of one source for one destination)
+_MIN_JOB_ROWS = 4            # a pusher job never has fewer rows than this
+
+
+def _reject(message):
+    raise ValueError(message)
+
+
 def validate_peer_count(peers):
     """The device barrier gives one lane of a single warp to every peer."""
-    if peers < 1 or peers > 32:
-        raise ValueError('The single-warp device barrier supports CP sizes from 1 to 32')
+    if peers not in range(1, _BARRIER_LANES + 1):
+        _reject('The single-warp device barrier supports CP sizes from 1 to 32')
 
 
 def validate_tile_n(mode, tile_n, output_width, peers, segment_width=0, num_segments=1, head_dim=0):
     """A scheduler tile may neither be truncated nor, when pushed, straddle a peer or head
     boundary. Receive traffic only permutes K, so it does not constrain the output tile
     (reference fused_gemm_a2a_kernels.py:43-59)."""
-    if mode not in ('push', 'recv') or tile_n <= 0 or output_width <= 0 or output_width % tile_n:
-        raise ValueError('GEMM mode must be push/recv and tile N must divide output width')
+    covers_width = tile_n > 0 and output_width > 0 and output_width % tile_n == 0
+    if mode not in ('push', 'recv') or not covers_width:
+        _reject('GEMM mode must be push/recv and tile N must divide output width')
     if num_segments not in (1, 3, 4):
-        raise ValueError('Expected one output projection or three/four QKV projections')
-    if num_segments > 1 and head_dim <= 0:
-        raise ValueError('QKV needs a positive head dimension')
-    if mode != 'push':
+        _reject('Expected one output projection or three/four QKV projections')
+    interleaved = num_segments > 1       # QKV(/gate): weight rows interleaved per head
+    if interleaved and head_dim <= 0:
+        _reject('QKV needs a positive head dimension')
+    if mode == 'recv':
         return
-    if peers <= 0 or segment_width <= 0 or segment_width % (peers * tile_n):
-        raise ValueError('Push segment width must be a multiple of CP * tile N')
-    if num_segments > 1 and tile_n != head_dim:
-        raise ValueError('QKV push needs one N tile per head')
+    routable = peers > 0 and segment_width > 0 and segment_width % (peers * tile_n) == 0
+    if not routable:
+        _reject('Push segment width must be a multiple of CP * tile N')
+    if interleaved and tile_n != head_dim:
+        _reject('QKV push needs one N tile per head')
 
 
 def mxfp8_tile_n(mode, output_width, peers=1, num_segments=1):
     """256-wide tiles only where they keep peer and head boundaries intact
     (reference fused_gemm_a2a_kernels.py:62-68)."""
-    if mode == 'push':
-        if num_segments > 1:
-            return 128
-        output_width //= peers
-    return 128 if output_width % 256 else 256
+    if mode == 'push' and num_segments > 1:
+        return 128                      # one tile per (head, segment) unit
+    span = output_width // peers if mode == 'push' else output_width
+    return 256 if span % 256 == 0 else 128
 
 
 def tile_swizzle(grouped_clusters, requested):
     """Raster group size that divides the cluster count exactly (no padding tiles): the gcd
     (reference fused_gemm_a2a_kernels.py:71-78)."""
-    if grouped_clusters < 1 or requested < 1:
-        raise ValueError('Cluster extent and FUSED_SWIZZLE must be positive')
+    if min(grouped_clusters, requested) < 1:
+        _reject('Cluster extent and FUSED_SWIZZLE must be positive')
     return math.gcd(grouped_clusters, requested)
 
 
@@ -72,26 +83,30 @@ def push_split(k, peers, segments, requested=0):
     """Row sub-blocks per (row block, destination) pusher job: jobs of roughly 64 KB, a power of
     two so the sub-blocks tile all 128 rows, at least four rows each
     (reference fused_gemm_a2a_kernels.py:81-97)."""
-    if peers < 1 or segments < 1 or k % (peers * segments):
-        raise ValueError('Receive K must split evenly over peers and input segments')
-    width = k // (peers * segments)
+    sources = peers * segments
+    if peers < 1 or segments < 1 or k % sources:
+        _reject('Receive K must split evenly over peers and input segments')
+    width = k // sources                 # BF16 columns one source contributes to a row
     if width % 64:
-        raise ValueError('The per-peer segment width must be a multiple of 64 BF16 elements')
+        _reject('The per-peer segment width must be a multiple of 64 BF16 elements')
     if requested:
         split = requested
     else:
-        split = min(CTA_M // 8, (CTA_M * width * 2) // 65536)
-        split = 1 if split < 1 else 1 << (split.bit_length() - 1)
-    if split < 1 or CTA_M % split or (CTA_M // split) % 4:
-        raise ValueError('FUSED_PUSH_SPLIT must divide 128 and leave at least four rows per job')
+        block_bytes = CTA_M * width * 2
+        wanted = min(CTA_M // 8, block_bytes // _JOB_BYTES)
+        split = 1 << (wanted.bit_length() - 1) if wanted >= 1 else 1     # round down to a power of two
+    whole_blocks = split >= 1 and CTA_M % split == 0
+    if not whole_blocks or (CTA_M // split) % _MIN_JOB_ROWS:
+        _reject('FUSED_PUSH_SPLIT must divide 128 and leave at least four rows per job')
     return split
 
 
 def padded_rows(valid, tile_m):
     """Rows a per-rank buffer holds for `valid` logical rows: rounded up to whole tiles."""
-    if valid < 1 or tile_m < 1:
-        raise ValueError('Token count and tile height must be positive')
-    return (valid + tile_m - 1) // tile_m * tile_m
+    if min(valid, tile_m) < 1:
+        _reject('Token count and tile height must be positive')
+    tiles = (valid + tile_m - 1) // tile_m
+    return tiles * tile_m
 
 
 # ----------------------------------------------------------------------------- launch helpers
