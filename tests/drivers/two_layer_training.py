@@ -28,7 +28,51 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 import torch.nn.functional as F  # noqa: E402
 
-LABELS = ('mb0/y', 'mb1/y', 'mb0/dx', 'mb1/dx', 'layer0/dw_qkv', 'layer0/dw_o', 'layer1/dw_qkv', 'layer1/dw_o')
+TENSORS = ('mb0/y', 'mb1/y', 'mb0/dx', 'mb1/dx', 'layer0/dw_qkv', 'layer0/dw_o', 'layer1/dw_qkv', 'layer1/dw_o')
+FIRST_WEIGHT_GRAD = 4          # from here on the tensors are partial sums over the CP group
+ELEMENT_TOLERANCE = 0.02       # |actual - expected| <= 0.02 * (peak + |expected|)
+RMS_TOLERANCE = 0.02           # relative RMS error
+
+
+def deviation(actual, expected):
+    """(max error over peak, relative RMS error, within tolerance) of one tensor."""
+    actual, expected = actual.float(), expected.float()
+    error = (actual - expected).abs()
+    peak = expected.abs().max().clamp_min(1e-12)
+    rms = (error.square().mean() / expected.square().mean().clamp_min(1e-24)).sqrt()
+    within = bool(torch.isfinite(actual).all()) and bool((error <= ELEMENT_TOLERANCE * (peak + expected.abs())).all())
+    return (error.max() / peak).item(), rms.item(), within and rms.item() <= RMS_TOLERANCE
+
+
+class DenseReference:
+    """The same two layers in FP32 on the gathered tokens of all ranks, rounding to BF16 where the
+    fused path does: after each projection, after attention, after the residual sum."""
+
+    def __init__(self, parameters, heads, head_dim):
+        self.weights = [w.detach().float().requires_grad_() for w in parameters]
+        self.heads, self.head_dim = heads, head_dim
+
+    def layer(self, x, w_qkv, w_out):
+        bf = torch.bfloat16
+        tokens = x.shape[0]
+        per_head = F.linear(x.float(), w_qkv).to(bf).view(tokens, self.heads, 3, self.head_dim)   # rows [q_h; k_h; v_h]
+        q, k, v = (per_head[:, :, i].float() for i in range(3))
+        probabilities = (torch.einsum('thd,shd->hts', q, k) * self.head_dim ** -0.5).softmax(-1)
+        attended = torch.einsum('hts,shd->thd', probabilities, v).to(bf)
+        return x + F.linear(attended.flatten(1).float(), w_out).to(bf)
+
+    def step(self, inputs, output_grads, rows):
+        """Expected (y per micro-batch, dx per micro-batch, dW per parameter); activations cut down
+        to this rank's rows, weight gradients complete."""
+        inputs = [x.requires_grad_() for x in inputs]
+        outputs = []
+        for x in inputs:
+            for w_qkv, w_out in zip(self.weights[0::2], self.weights[1::2]):
+                x = self.layer(x, w_qkv, w_out)
+            outputs.append(x)
+        grads = torch.autograd.grad(outputs, (*inputs, *self.weights), output_grads)
+        n = len(inputs)
+        return [y[rows] for y in outputs] + [g[rows] for g in grads[:n]] + list(grads[n:])
 
 
 def run(dev, hidden=1024, heads=8, total_tokens=512, replays=2):
@@ -37,113 +81,104 @@ def run(dev, hidden=1024, heads=8, total_tokens=512, replays=2):
     from fused_gemm_a2a import FusedGemmA2AWorkspace, FusedOutputProjection, FusedQKVProjection
     cp, rank = dist.get_world_size(), dist.get_rank()
     assert total_tokens % cp == 0 and heads % cp == 0
-    head_dim = hidden // heads
-    local = total_tokens // cp
-    rows = slice(rank * local, (rank + 1) * local)
+    head_dim, local = hidden // heads, total_tokens // cp
+    my_rows = slice(rank * local, (rank + 1) * local)
     bf = torch.bfloat16
-    gen = torch.Generator(device='cpu').manual_seed(1234)   # parameters: identical on every rank
 
-    def weight(n_rows):
-        return torch.nn.Parameter((torch.randn(n_rows, hidden, generator=gen) * hidden ** -0.5).to(bf).to(dev))
+    shared = torch.Generator(device='cpu').manual_seed(1234)      # parameters: identical on every rank
+    private = torch.Generator(device='cpu').manual_seed(5678 + rank)
 
-    layers = [(FusedQKVProjection(hidden, heads, weight=weight(3 * hidden)),
-               FusedOutputProjection(hidden, heads, weight=weight(hidden))) for _ in range(2)]
-    workspace = FusedGemmA2AWorkspace(hidden, heads, local)
-    parameters = tuple(module.weight for layer in layers for module in layer)
-    reference_weights = [w.detach().float().requires_grad_() for w in parameters]
-    gen = torch.Generator(device='cpu').manual_seed(5678 + rank)
-    xs = [torch.randn(local, hidden, generator=gen).to(bf).to(dev).requires_grad_() for _ in range(2)]
-    dys = [torch.randn(local, hidden, generator=gen).to(bf).to(dev) for _ in range(2)]
+    def parameter(out_rows):
+        values = torch.randn(out_rows, hidden, generator=shared) * hidden ** -0.5
+        return torch.nn.Parameter(values.to(bf).to(dev))
 
-    def attention(q, k, v):      # [P*M, N/P, D] each: all tokens, this rank's heads
-        o = F.scaled_dot_product_attention(q.transpose(0, 1), k.transpose(0, 1), v.transpose(0, 1))
-        return o.transpose(0, 1).contiguous()
+    def activation(requires_grad):
+        return torch.randn(local, hidden, generator=private).to(bf).to(dev).requires_grad_(requires_grad)
+
+    layers = [(FusedQKVProjection(hidden, heads, weight=parameter(3 * hidden)),
+               FusedOutputProjection(hidden, heads, weight=parameter(hidden))) for _ in range(2)]
+    workspace = FusedGemmA2AWorkspace(hidden, heads, local)      # one workspace for both layers
+    parameters = [module.weight for layer in layers for module in layer]
+    reference = DenseReference(parameters, heads, head_dim)
+    xs = [activation(True) for _ in range(2)]
+    dys = [activation(False) for _ in range(2)]
+
+    def attend(q, k, v):         # [P*M, N/P, D] each: every token, this rank's heads
+        by_head = [t.transpose(0, 1) for t in (q, k, v)]
+        return F.scaled_dot_product_attention(*by_head).transpose(0, 1).contiguous()
 
     def fused_step():
-        ys = []
+        """Both micro-batches go forward through both layers before anything goes backward."""
+        outputs = []
         for x in xs:
             for qkv, proj in layers:
                 q, k, v = qkv(x, workspace)
-                for tensor, buffer in zip((q, k, v), workspace._view(local, 3).heads):
-                    assert tensor.untyped_storage().data_ptr() != buffer.untyped_storage().data_ptr()
-                x = x + proj(attention(q, k, v), workspace)
-            ys.append(x)
-        gradients = torch.autograd.grad(ys, (*xs, *parameters), dys)
-        return (*ys, *gradients)
+                shared_buffers = {buffer.untyped_storage().data_ptr() for buffer in workspace._view(local, 3).heads}
+                assert not shared_buffers & {t.untyped_storage().data_ptr() for t in (q, k, v)}   # outputs are owned
+                x = x + proj(attend(q, k, v), workspace)
+            outputs.append(x)
+        return [*outputs, *torch.autograd.grad(outputs, (*xs, *parameters), dys)]
 
-    def gather(t):
+    def all_ranks(t):
         parts = [torch.empty_like(t) for _ in range(cp)]
         dist.all_gather(parts, t.detach().contiguous())
         return torch.cat(parts)
 
-    def reference_step():
-        inputs = [gather(x).requires_grad_() for x in xs]
-        gradients = [gather(dy) for dy in dys]
-        ys = []
-        for x in inputs:
-            for wqkv, wo in zip(reference_weights[::2], reference_weights[1::2]):
-                packed = F.linear(x.float(), wqkv).to(bf)
-                q, k, v = packed.view(total_tokens, heads, 3, head_dim).unbind(2)
-                scores = torch.einsum('thd,shd->hts', q.float(), k.float()) * head_dim ** -0.5
-                o = torch.einsum('hts,shd->thd', scores.softmax(-1), v.float()).to(bf)
-                x = x + F.linear(o.flatten(1).float(), wo).to(bf)
-            ys.append(x)
-        grads = torch.autograd.grad(ys, (*inputs, *reference_weights), gradients)
-        return (*(y[rows] for y in ys), *(g[rows] for g in grads[:2]), *grads[2:])
+    def expected_step():
+        return reference.step([all_ranks(x) for x in xs], [all_ranks(dy) for dy in dys], my_rows)
 
     failures, errors = [], {}
 
-    def check(actuals, expected, label):
-        for i, (actual, ref, name) in enumerate(zip(actuals, expected, LABELS)):
-            if i >= 4:                       # weight gradients are partial sums over the CP group
-                actual = actual.float().clone()
-                dist.all_reduce(actual)
-            actual, ref = actual.float(), ref.float()
-            delta = (actual - ref).abs()
-            peak = ref.abs().max().clamp_min(1e-12)
-            rms = delta.square().mean().sqrt() / ref.square().mean().sqrt().clamp_min(1e-12)
-            good = torch.isfinite(actual).all() & (delta <= 0.02 * (peak + ref.abs())).all() & (rms <= 0.02)
-            errors[f'{label}/{name}'] = dict(max_error_over_peak=(delta.max() / peak).item(), relative_rms=rms.item())
-            if not good.item():
-                failures.append(f'{label}/{name}: {errors[f"{label}/{name}"]}')
+    def check(stage, actual, expected):
+        for index, (name, got, want) in enumerate(zip(TENSORS, actual, expected)):
+            if index >= FIRST_WEIGHT_GRAD:
+                got = got.float().clone()
+                dist.all_reduce(got)
+            peak_error, rms, ok = deviation(got, want)
+            errors[f'{stage}/{name}'] = dict(max_error_over_peak=peak_error, relative_rms=rms)
+            if not ok:
+                failures.append(f'{stage}/{name}: {errors[f"{stage}/{name}"]}')
+
+    def device_errors():
+        torch.cuda.synchronize()
+        status = workspace.comm.status.tolist()
+        if status[0]:
+            failures.append(f'device status {status}')
 
     previous_tf32 = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
-        expected = reference_step()
-        check(fused_step(), expected, 'eager')
+        expected = expected_step()
+        check('eager', fused_step(), expected)
         # Saved-tensor hooks (activation offloading and the like) hand backward plain tensors in
         # place of Parameters; main_grad and the other metadata must still come from the module's
         # own Parameter (reference fused_gemm_a2a.py:348-351, tests/mxfp8_driver.py:136-138).
         with torch.autograd.graph.saved_tensors_hooks(lambda t: t.detach(), lambda t: t):
-            check(fused_step(), expected, 'hooks')
-        torch.cuda.synchronize()
-        if workspace.comm.status.tolist()[0]:
-            failures.append(f'device status {workspace.comm.status.tolist()}')
+            check('hooks', fused_step(), expected)
+        device_errors()
         anybody_failed = torch.tensor([len(failures)], dtype=torch.int32, device=dev)
         dist.all_reduce(anybody_failed, op=dist.ReduceOp.MAX)   # every rank takes the same branch
         if replays and anybody_failed.item() == 0:
-            stream = torch.cuda.Stream()
-            stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(stream):
-                fused_step()
-            stream.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fused_step()                 # warm-up on the capture stream
+            side.synchronize()
             dist.barrier()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+            with torch.cuda.graph(graph, stream=side):
                 captured = fused_step()
-            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.current_stream().wait_stream(side)
             for replay in range(replays):
                 with torch.no_grad():
                     for t in (*xs, *dys):
-                        t.normal_()
+                        t.normal_()          # new inputs in place: the graph reads the same storage
                 torch.cuda.synchronize()
                 dist.barrier()
                 graph.replay()
                 torch.cuda.synchronize()
-                check(captured, reference_step(), f'graph{replay}')
-                if workspace.comm.status.tolist()[0]:
-                    failures.append(f'device status {workspace.comm.status.tolist()}')
+                check(f'graph{replay}', captured, expected_step())
+                device_errors()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = previous_tf32
     return failures, errors
