@@ -1,0 +1,200 @@
+"""A CPU stand-in for libfga.so, for host-layer tests only.
+
+TEST INFRASTRUCTURE. The library has no CPU path and the package never imports this file. It lets
+the Python layer (workspace, views, autograd functions) run end to end on CPU ranks under gloo, so
+that what the layer does with the C ABI - buffer carving, peer tables, call order, bias placement,
+padding, ownership copies, main_grad protocol - can be checked numerically against the oracle
+without a GPU, for one rank and for several.
+
+How: every entry point of include/fga.h that the layer reaches is restated here with plain torch
+on host memory, following the header's contract (not the CUDA sources):
+  * symmetric memory is POSIX shared memory; the 64-byte handle carries its name, so a peer's
+    allocation is really mapped into this process and remote stores really land there;
+  * a group barrier is a gloo barrier; the recv GEMM's wait for arrival counters is a gloo barrier
+    between its pushing half and its computing half (each simulated "kernel" runs to completion
+    on the host, so this is the only point where ranks must meet);
+  * GEMMs accumulate in FP32 from the BF16 values and round once, the arithmetic of the oracle.
+BF16 only; the MXFP8 launch plan is covered by the call traces (tests/host_trace.py).
+"""
+import ctypes
+import os
+from multiprocessing import shared_memory
+
+import torch
+import torch.distributed as dist
+
+from host_trace import _TorchShim   # torch as seen from inside the package: the CPU is "the device"
+
+BF16 = torch.bfloat16
+
+
+def _bytes_at(address, nbytes):
+    return (ctypes.c_char * nbytes).from_address(int(address))
+
+
+def matrix(address, rows, cols, dtype=BF16):
+    """A [rows, cols] tensor over raw host memory."""
+    itemsize = torch.empty(0, dtype=dtype).element_size()
+    return torch.frombuffer(_bytes_at(address, rows * cols * itemsize), dtype=dtype).view(rows, cols)
+
+
+def table(address, entries):
+    return list((ctypes.c_int64 * entries).from_address(int(address)))
+
+
+class SimulatedLibrary:
+    def __init__(self, tag):
+        self.tag = tag                    # unique per test run: names of the shared segments
+        self.rank = dist.get_rank()
+        self.segments = []                # SharedMemory objects this process created or opened
+        self.created = []
+        self.launches = 0
+
+    def fga_last_error(self):
+        return b'simulated library: a receive row block did not collect all of its arrivals'
+
+    # ---- symmetric memory
+    def _map(self, segment):
+        self.segments.append(segment)
+        return ctypes.addressof(ctypes.c_char.from_buffer(segment.buf))
+
+    def fga_symm_alloc(self, nbytes, out):
+        name = f'{self.tag}_{self.rank}_{len(self.created)}'
+        segment = shared_memory.SharedMemory(name=name, create=True, size=max(int(nbytes), 16))
+        segment.buf[:] = bytes(len(segment.buf))
+        self.created.append(segment)
+        out._obj.value = self._map(segment)
+        return 0
+
+    def fga_symm_export(self, base, handle):
+        index = [ctypes.addressof(ctypes.c_char.from_buffer(s.buf)) for s in self.created].index(base.value)
+        name = self.created[index].name.encode()
+        ctypes.memmove(handle, name + bytes(64 - len(name)), 64)
+        return 0
+
+    def fga_symm_open(self, raw, out):
+        out._obj.value = self._map(shared_memory.SharedMemory(name=raw.rstrip(b'\0').decode()))
+        return 0
+
+    def close(self, meet=True):
+        if meet:
+            dist.barrier()             # nobody unmaps while a peer may still store into the segment
+        self.segments.clear()
+        import gc
+        gc.collect()
+        for segment in self.created:
+            try:
+                segment.close()
+            except BufferError:        # a tensor still views the mapping; the name is removed all the same
+                pass
+            try:
+                segment.unlink()
+            except FileNotFoundError:
+                pass
+
+    # ---- fused GEMMs (contract: include/fga.h)
+    def fga_gemm_push(self, a, m, k, a_rows, b, b_is_kn, bias, segments, n_segment, tables, head_rows,
+                      rank, p, status, timeout, stream):
+        self.launches += 1
+        n = segments * n_segment
+        padded = torch.zeros(a_rows, k, dtype=BF16)
+        padded[:m] = matrix(a, m, k)
+        weight = matrix(b, k, n).t() if b_is_kn else matrix(b, n, k)
+        product = padded.float() @ weight.float().t()
+        if bias:
+            product = product + matrix(bias, 1, n).float()
+        product = product.to(BF16)
+        heads_per_rank = n_segment // p // 128
+        for unit in range(n // 128):                       # one 128-column (head, segment) unit at a time
+            head, segment = (unit // segments, unit % segments) if segments > 1 else (unit, 0)
+            dest, within = head // heads_per_rank, head % heads_per_rank
+            target = matrix(table(tables[segment], p)[dest], p * head_rows, n_segment // p)
+            target[rank * head_rows:rank * head_rows + a_rows, within * 128:(within + 1) * 128] = \
+                product[:, unit * 128:(unit + 1) * 128]
+        return 0
+
+    def fga_gemm_recv(self, recv, recv_rows, k, b, b_is_kn, n, c, peer_recv, peer_counters, counters,
+                      srcs, num_in, src_rows, split, rank, p, roles, epoch, progress, status, timeout, stream):
+        self.launches += 1
+        heads_per_rank = k // (p * num_in * 128)
+        for turn in range(p if roles & 2 else 0):
+            # One rank pushes at a time: the counter increments below are plain read-modify-writes
+            # on memory that every rank maps (the GPU uses atomic reductions).
+            if turn != rank:
+                dist.barrier()
+                continue
+            for dest in range(p):
+                target = matrix(table(peer_recv, p)[dest], recv_rows, k)
+                arrivals = torch.frombuffer(_bytes_at(table(peer_counters, p)[dest], 4 * (recv_rows // 128)),
+                                            dtype=torch.int32)
+                for t in range(num_in):
+                    source = matrix(srcs[t], p * src_rows, heads_per_rank * 128)[dest * src_rows:(dest + 1) * src_rows]
+                    for unit in range(heads_per_rank):
+                        column = ((rank * heads_per_rank + unit) * num_in + t) * 128
+                        target[:src_rows, column:column + 128] = source[:, unit * 128:(unit + 1) * 128]
+                        target[src_rows:, column:column + 128] = 0
+                    arrivals += split          # `split` jobs per (row block, source, destination)
+            dist.barrier()                     # after the last turn: every row block has all its arrivals
+        if not roles & 2:
+            dist.barrier()
+        if roles & 1:
+            own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
+            if roles & 2 and not bool((own == p * num_in * split).all()):
+                return -2
+            weight = matrix(b, k, n).t() if b_is_kn else matrix(b, n, k)
+            matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ weight.float().t()).to(BF16)
+        return 0
+
+
+def install(fused, tag):
+    """Patch the package to run on the simulated library; returns (library, undo)."""
+    import _fga_native
+    from oracle.ulysses_oracle import reduce_bias_grad_ref, resize_rank_rows_ref
+    sim = SimulatedLibrary(tag)
+    names = ('device_barrier', 'resize_rank_rows', 'reduce_bias_grad', 'bf16_wgrad')
+    saved = {name: getattr(fused, name) for name in names}
+    saved.update(lib=_fga_native.lib, torch=fused.torch, wrap=fused._wrap)
+    _fga_native.lib = lambda: sim
+    fused.torch = _TorchShim()
+    fused._wrap = lambda address, nbytes, _device: torch.frombuffer(_bytes_at(address, nbytes), dtype=torch.uint8)
+
+    def device_barrier(flags, peer_flags, rank, peers, status, *, bump=False, counters=None, epoch=None):
+        sim.launches += 1
+        if bump and counters is not None:
+            counters.zero_()               # before publishing: nobody can have incremented them yet
+        dist.barrier()
+        if bump and epoch is not None:
+            epoch += 1
+
+    def resize_rank_rows(tensors, peers, rows, *, copy=False, bias=None, head_dim=128, head_offset=0, use_cute=False):
+        sim.launches += 1
+        return resize_rank_rows_ref(tuple(tensors), peers, rows, bias=bias, head_dim=head_dim, head_offset=head_offset)
+
+    def reduce_bias_grad(dy, out, *, accumulate=False, use_cute=False):
+        sim.launches += 1
+        out.copy_(reduce_bias_grad_ref(dy, out.dtype, previous=out if accumulate else None))
+        return out
+
+    def bf16_wgrad(dy, x, out, status, *, accumulate=False):
+        sim.launches += 1
+        product = dy.float().t() @ x.float()
+        out.copy_((out.float() + product) if accumulate else product)
+        return out
+
+    for fn in (device_barrier, resize_rank_rows, reduce_bias_grad, bf16_wgrad):
+        setattr(fused, fn.__name__, fn)
+
+    def undo(meet=True):
+        sim.close(meet)
+        _fga_native.lib = saved['lib']
+        fused.torch, fused._wrap = saved['torch'], saved['wrap']
+        for name in names:
+            setattr(fused, name, saved[name])
+        fused._Comm._instances.clear()
+        fused._placeholder_grads.clear()
+
+    return sim, undo
+
+
+def unique_tag():
+    return f'fga{os.getpid() % 100000}'

@@ -1,0 +1,185 @@
+"""The host layer end to end on CPU ranks (gloo, world size 1, 2 and 4) against the oracle.
+
+libfga.so is replaced by tests/abi_simulator.py: shared-memory "symmetric" buffers, gloo barriers,
+torch GEMMs, all following the contract of include/fga.h. Everything above the C ABI is the real
+package: workspace construction and handle exchange, slab carving, peer tables, the autograd
+functions with their bias, padding, ownership and main_grad handling. Checked per rank: the public
+outputs and gradients against the oracle (same tolerance as the GPU tests: max error 1e-2 of the
+scale, Frobenius 2e-3), the transport buffers bit for bit including zeroed pad rows, the arrival
+counters, and that outputs own their storage.
+"""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+BF = torch.bfloat16
+
+CASES = (dict(gate=False, bias=False, bias_in_gemm=False, main_grad=False),
+         dict(gate=True, bias=True, bias_in_gemm=False, main_grad=False),
+         dict(gate=False, bias=True, bias_in_gemm=True, main_grad=True))
+
+
+def close(actual, expected, what):
+    actual, expected = actual.detach().float(), expected.detach().float()
+    assert actual.shape == expected.shape, f'{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}'
+    scale = expected.abs().max().clamp_min(1e-6)
+    assert (actual - expected).abs().max() <= 1e-2 * scale, f'{what}: max error'
+    assert torch.linalg.norm(actual - expected) <= 2e-3 * torch.linalg.norm(expected) + 1e-6, f'{what}: Frobenius'
+
+
+def same(actual, expected, what):
+    """Bit-for-bit equality, with the place of the first difference in the message."""
+    assert actual.shape == expected.shape, f'{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}'
+    if not torch.equal(actual, expected):
+        where = (actual != expected).nonzero()
+        raise AssertionError(f'{what}: {len(where)} elements differ, first at {where[0].tolist()} '
+                             f'({actual[tuple(where[0])].item()} vs {expected[tuple(where[0])].item()}), '
+                             f'last at {where[-1].tolist()}')
+
+
+def landed(buffer, expected, tokens, capacity, what):
+    """A head-side buffer [P*capacity, width] after a push: GEMM results (FP32 sums in another
+    order than the oracle's, so BF16 values may differ in the last bit) in the logical rows of every
+    source rank, and exactly the oracle's pad rows (zeros, or the bias when the GEMM adds it)."""
+    close(buffer, expected, what)
+    pad = torch.ones(buffer.shape[0], dtype=torch.bool)
+    for source in range(buffer.shape[0] // capacity):
+        pad[source * capacity:source * capacity + tokens] = False
+    same(buffer[pad], expected[pad], what + ' pad rows')
+
+
+def everyone(value):
+    box = [None] * dist.get_world_size()
+    dist.all_gather_object(box, value)
+    return box
+
+
+def run_rank(hidden, heads, capacity_tokens, token_counts):
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    from oracle.ulysses_oracle import UlyssesOracle
+    p, rank = dist.get_world_size(), dist.get_rank()
+    d = hidden // heads
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    completed = False
+    try:
+        for case in CASES:
+            segments = 4 if case['gate'] else 3
+            g = torch.Generator().manual_seed(4321)            # parameters: the same on every rank
+            wq = (torch.randn(segments * hidden, hidden, generator=g) / 32).to(BF)
+            wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+            bq = torch.randn(segments * hidden, generator=g).mul(0.5).to(BF) if case['bias'] else None
+            bo = torch.randn(hidden, generator=g).mul(0.5).to(BF) if case['bias'] else None
+            params = dict(wq=wq.clone().requires_grad_(), wo=wo.clone().requires_grad_(),
+                          bq=None if bq is None else bq.clone().requires_grad_(),
+                          bo=None if bo is None else bo.clone().requires_grad_())
+            start = {}
+            if case['main_grad']:
+                for name, param in params.items():
+                    if param is not None:
+                        start[name] = torch.randn(param.shape, generator=g)
+                        param.main_grad = start[name].clone()
+            ws = fused.FusedGemmA2AWorkspace(hidden, heads, capacity_tokens, gate=case['gate'])
+            qkv = fused.FusedQKVProjection(hidden, heads, weight=params['wq'], bias=params['bq'], gate=case['gate'],
+                                           bias_in_gemm=case['bias_in_gemm'])
+            proj = fused.FusedOutputProjection(hidden, heads, weight=params['wo'], bias=params['bo'])
+            oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, bias_in_gemm=case['bias_in_gemm'])
+            accumulated = {name: torch.zeros_like(t) for name, t in start.items()}
+            for tokens in token_counts:
+                g = torch.Generator().manual_seed(1000 * tokens + rank)
+                x = torch.randn(tokens, hidden, generator=g).to(BF).requires_grad_()
+                grads = [torch.randn(p * tokens, heads // p, d, generator=g).to(BF) for _ in range(segments)]
+                o = torch.randn(p * tokens, heads // p, d, generator=g).to(BF).requires_grad_()
+                dy = torch.randn(tokens, hidden, generator=g).to(BF)
+                outs = qkv(x, ws)
+                view = ws._view(tokens, segments)
+                cap = view.capacity
+                xs = everyone(x.detach())
+                # head-side buffers right after the push: every rank's tile landed where the oracle puts it
+                for seg, want in enumerate(oracle.qkv_heads_buffers(xs, cap)[rank]):
+                    landed(view.heads[seg], want, tokens, cap, f'head buffer {seg}')
+                got = torch.autograd.grad(outs, [x, params['wq']] + ([params['bq']] if case['bias'] else []), grads)
+                all_grads = everyone(tuple(grads))
+                same(view.recv, oracle.qkv_recv_buffer(all_grads, rank, cap), 'QKV dgrad transport')
+                assert view.counters.tolist() == [p * segments * fused._Comm.push_split(view.recv, segments, p)] * (cap // 128)
+                for name, t, want in zip('qkvg', outs, oracle.qkv_forward(xs)[rank]):
+                    close(t, want, f'{name} tokens={tokens}')
+                    assert t.shape == (p * tokens, heads // p, d)
+                    assert t.untyped_storage().data_ptr() not in {h.untyped_storage().data_ptr() for h in view.heads}
+                rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
+                close(got[0], rdx, 'dx')
+                y = proj(o, ws)
+                all_o = everyone(o.detach())
+                out_view = ws._view(tokens, 1)
+                same(out_view.recv, oracle.out_recv_buffer(all_o, rank, cap), 'output transport')
+                close(y, oracle.out_forward(all_o)[rank], 'y')
+                got_out = torch.autograd.grad(y, [o, params['wo']] + ([params['bo']] if case['bias'] else []), dy)
+                dys = everyone(dy)
+                landed(out_view.heads[0], oracle.out_dhead_buffers(dys, cap)[rank], tokens, cap, 'dO head buffer')
+                rdos, rparams = oracle.out_backward(all_o, dys)
+                close(got_out[0], rdos[rank], 'dO')
+                if case['main_grad']:
+                    accumulated['wq'] += rdw
+                    accumulated['wo'] += rparams[rank][0]
+                    accumulated['bq'] += rdb
+                    accumulated['bo'] += rparams[rank][1]
+                    assert params['wq'].grad_added_to_main_grad and params['wo'].grad_added_to_main_grad
+                    assert got[1].shape == wq.shape and got_out[1].shape == wo.shape     # placeholders
+                else:
+                    close(got[1], rdw, 'dW_qkv')
+                    close(got_out[1], rparams[rank][0], 'dW_o')
+                    if case['bias']:
+                        close(got[2], rdb, 'dbias_qkv')
+                        close(got_out[2], rparams[rank][1], 'dbias_o')
+            for name, total in accumulated.items():
+                close(params[name].main_grad - start[name], total, f'main_grad of {name}')
+        completed = True
+        return sim.launches
+    finally:
+        undo(meet=completed)     # after a failure the peers are not at the same point: do not wait for them
+
+
+def worker(rank, world, port, queue):
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    try:
+        launches = run_rank(hidden=512, heads=4, capacity_tokens=300, token_counts=(300, 129, 1))
+        queue.put((rank, 'ok', launches))
+    except BaseException as error:   # report and leave at once; the parent stops the peers
+        import traceback
+        queue.put((rank, 'fail', f'{type(error).__name__}: {error}\n{traceback.format_exc()[-2500:]}'))
+        queue.close()
+        queue.join_thread()
+        os._exit(1)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [1, 2, 4])
+def test_modules_on_simulated_ranks_match_the_oracle(world):
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, world, 29660 + world, queue)) for r in range(world)]
+    for proc in procs:
+        proc.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(queue.get(timeout=600))
+            assert results[-1][1] == 'ok', f'rank {results[-1][0]}: {results[-1][2]}'
+    finally:
+        for proc in procs:
+            proc.join(timeout=5 if results and results[-1][1] != 'ok' else 120)
+            if proc.is_alive():
+                proc.terminate()
+    for rank, verdict, detail in sorted(results):
+        # 3 cases x 3 token counts x (6 barriers + 4 GEMMs + 2 weight gradients + 2 row copies [+ bias reductions])
+        assert detail >= 3 * 3 * 14
