@@ -108,27 +108,9 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams P, cu
 static int choose_k_splits(long long tiles, int k_tiles, int pairs) {
   const char* v = getenv("FGA_WGRAD_SPLITS");
   if (v == nullptr || *v == '\0') return 1;
-  const bool automatic = strcmp(v, "auto") == 0;
-  const int forced = automatic ? 0 : atoi(v);
-  if (!automatic && forced <= 1) return 1;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; ++s) {
-    if (s > 1 && k_tiles / s < 32) break;
-    if (!automatic) {
-      best = s;  // the largest allowed count up to the forced one
-      if (s == forced) break;
-      continue;
-    }
-    const long long units = tiles * s;
-    const double eff = static_cast<double>(units) / (static_cast<double>((units + pairs - 1) / pairs) * pairs);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
-      best = s;
-    }
-    if (eff >= 0.97) break;
-  }
-  return best;
+  if (strcmp(v, "auto") == 0) return sched::pick_k_splits(tiles, k_tiles, pairs, 0);
+  const int forced = atoi(v);
+  return forced <= 1 ? 1 : sched::pick_k_splits(tiles, k_tiles, pairs, forced);
 }
 
 // Block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 across the pair, N = bn.
@@ -230,18 +212,9 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   P.k_tiles = k / kTileK;
   P.group_m = env_int("FGA_GROUP_M_RECV", 4);
   P.stages = kMaxStages - 1;  // the sixth stage's shared memory holds the pusher buffers
-  {
-    // Pusher chunking: a chunk is `push_rows` rows of `push_units` 256-byte head units, at most
-    // one 4 KiB buffer. Rows wider than a buffer are cut into equal pieces of whole units.
-    const int hpr = k / (p * num_in * 128), sub_rows = 128 / split;
-    int units = hpr;
-    while (units > kPushBufBytes / 256 || hpr % units) --units;
-    int rows = 1;
-    if (units == hpr)
-      while (rows * 2 * units * 256 <= kPushBufBytes && rows * 2 <= sub_rows) rows *= 2;
-    P.push_units = units;
-    P.push_rows = rows;
-  }
+  // Pusher chunking: a chunk is `push_rows` rows of `push_units` 256-byte head units, at most
+  // one 4 KiB buffer. Rows wider than a buffer are cut into equal pieces of whole units.
+  sched::push_chunking(k / (p * num_in * 128), 128 / split, kPushBufBytes, P.push_units, P.push_rows);
   P.a_mn = 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
@@ -458,16 +431,7 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   P.k_tiles = k / 128;
   P.group_m = env_int("FGA_GROUP_M_RECV", 4);
   P.stages = kMaxStages - 1;
-  {
-    const int hpr = k / (p * num_in * 128), sub_rows = 128 / split;
-    int units = hpr;
-    while (units > kPushBufBytes / 256 || hpr % units) --units;
-    int rows = 1;
-    if (units == hpr)
-      while (rows * 2 * units * 256 <= kPushBufBytes && rows * 2 <= sub_rows) rows *= 2;
-    P.push_units = units;
-    P.push_rows = rows;
-  }
+  sched::push_chunking(k / (p * num_in * 128), 128 / split, kPushBufBytes, P.push_units, P.push_rows);
   P.idesc = make_idesc_mx(P.bn);
   P.rank = rank;
   P.p = p;

@@ -26,6 +26,7 @@
 #include "ptx.cuh"
 #include "common.cuh"
 #include "mx_quant.cuh"
+#include "schedule.cuh"
 
 namespace fga {
 
@@ -181,42 +182,20 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
   return __uint_as_float(bits16 << 16);
 }
 
-// Tile t of this pair's sequence -> (pair tile along M, tile along N). N varies fastest inside a
-// group of `group_m` pair tiles, so a wave of CTAs stays within a few row blocks (the recv GEMM
-// can start before later blocks arrive; a push wave spreads its stores over all destinations) and
-// each weight tile is reused across the group out of L2.
+// The index arithmetic lives in schedule.cuh (shared with the host and the CPU tests); these are
+// the kernel's views of it.
 __device__ __forceinline__ void tile_coords(const GemmParams& P, int t, int& m, int& n) {
-  const int per_group = P.group_m * P.n_tiles;
-  const int g = t / per_group;
-  const int r = t - g * per_group;
-  const int gm = min(P.group_m, P.m_tiles - g * P.group_m);
-  n = r / gm;
-  m = g * P.group_m + (r - n * gm);
+  sched::tile_coords(P.m_tiles, P.n_tiles, P.group_m, t, m, n);
 }
 
-// Work unit u of the grid's sequence -> (output tile, K-step range). With k_splits > 1 the split
-// index varies slowest, so a wave of CTA pairs works on one K range and the operands it shares
-// stay in L2; every unit adds its partial tile into the FP32 output with bulk reductions.
 __device__ __forceinline__ void unit_coords(const GemmParams& P, int u, int total_tiles, int& t, int& kt0,
                                             int& kt1) {
-  if (P.k_splits <= 1) {
-    t = u;
-    kt0 = 0;
-    kt1 = P.k_tiles;
-    return;
-  }
-  const int s = u / total_tiles;
-  t = u - s * total_tiles;
-  kt0 = static_cast<int>(static_cast<long long>(s) * P.k_tiles / P.k_splits);
-  kt1 = static_cast<int>(static_cast<long long>(s + 1) * P.k_tiles / P.k_splits);
+  sched::unit_coords(P.k_tiles, P.k_splits, total_tiles, u, t, kt0, kt1);
 }
 
 // First B row (weight row / output column) of N tile n. Push mode rotates the N order by rank.
 __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
-  if (P.mode == kPush) {
-    n += P.n_rotate;
-    if (n >= P.n_tiles) n -= P.n_tiles;
-  }
+  if (P.mode == kPush) n = sched::rotated_n(n, P.n_rotate, P.n_tiles);
   return n * P.bn;
 }
 
@@ -246,13 +225,8 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
   uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
   auto do_job = [&](long long job) {
-    const int mi = static_cast<int>(job / jobs_per_block);
-    int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
-    const int q = rest % P.split;
-    rest /= P.split;
-    const int d = (rest % P.p + P.rank) % P.p;
-    const int t = rest / P.p;
-    const int row0 = mi * kTileM + q * sub_rows;
+    const sched::PushJob j = sched::decode_push_job(job, P.num_in, P.p, P.split, P.rank);
+    const int mi = j.mi, t = j.t, d = j.d, row0 = j.row0;
     if (paced) {
       // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
       // the same schedule, so the peers consume at about this rank's pace; pushing faster only
@@ -278,17 +252,10 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
                       (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
     char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
     for (int c = 0; c < chunks_per_job; ++c) {
-      int r0, u0;
-      if (pieces_per_row == 1) {
-        r0 = c * rpc;
-        u0 = 0;
-      } else {
-        r0 = c / pieces_per_row;
-        u0 = (c - r0 * pieces_per_row) * upp;
-      }
+      const sched::PushChunk ch = sched::push_chunk(c, hpr, upp, rpc, P.src_rows, row0);
+      const int r0 = ch.r0, u0 = ch.u0, valid = ch.valid;  // valid: rows that exist in the source
       const int b = issued & 1;
       const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
-      const int valid = max(0, min(rpc, P.src_rows - (row0 + r0)));  // rows that exist in the source
       if (lane == 0) bulk_wait_read<1>();  // the group that used this buffer last has left shared memory
       __syncwarp();
       if (lane == 0 && valid > 0) {
@@ -311,11 +278,11 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
           for (int r = 0; r < rpc; ++r) {
             char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
             if (P.num_in == 1) {
-              bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
+              bulk_store(drow + sched::recv_column(P.rank, hpr, u0, 1, 0) * 2, buf + r * chunk_row_bytes,
                          chunk_row_bytes);
             } else {
               for (int u = 0; u < upp; ++u) {
-                const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
+                const long long col = sched::recv_column(P.rank, hpr, u0 + u, P.num_in, t);
                 bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
               }
             }
@@ -341,8 +308,7 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   // raster groups, which the GEMM cannot start without; afterwards only `push_warps` warps per CTA
   // continue, enough to stay ahead of the GEMM without saturating the NVLink egress queue that
   // the GEMM's own loads share. `steady` is false when CTAs that only push take that part over.
-  const long long first_jobs =
-      min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
+  const long long first_jobs = sched::first_phase_jobs(P.m_tiles, P.group_m, P.num_in, P.p, P.split);
   for (long long job = blockIdx.x * kPusherWarps + pusher; job < first_jobs && !w.dead;
        job += static_cast<long long>(gridDim.x) * kPusherWarps)
     do_job(job);
@@ -381,13 +347,8 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
   const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
   uint32_t seq = ring.seq, parity = ring.parity;
   for (long long job = job_begin; job < job_end && !w.dead; job += job_stride) {
-    const int mi = static_cast<int>(job / jobs_per_block);
-    int rest = static_cast<int>(job - static_cast<long long>(mi) * jobs_per_block);
-    const int q = rest % P.split;
-    rest /= P.split;
-    const int d = (rest % P.p + P.rank) % P.p;
-    const int t = rest / P.p;
-    const int row0 = mi * kTileM + q * sub_rows;
+    const sched::PushJob j = sched::decode_push_job(job, P.num_in, P.p, P.split, P.rank);
+    const int mi = j.mi, t = j.t, d = j.d, row0 = j.row0;
     if (paced) {
       // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
       // the same schedule, so the peers consume at about this rank's pace; pushing faster only
@@ -414,14 +375,10 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
     char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
     // Chunk c of the job: rows [r0, r0 + rpc) x head units [u0, u0 + upp); `valid` rows exist in the source.
     auto geometry = [&](int c, int& r0, int& u0, int& valid) {
-      if (pieces_per_row == 1) {
-        r0 = c * rpc;
-        u0 = 0;
-      } else {
-        r0 = c / pieces_per_row;
-        u0 = (c - r0 * pieces_per_row) * upp;
-      }
-      valid = max(0, min(rpc, P.src_rows - (row0 + r0)));
+      const sched::PushChunk ch = sched::push_chunk(c, hpr, upp, rpc, P.src_rows, row0);
+      r0 = ch.r0;
+      u0 = ch.u0;
+      valid = ch.valid;
     };
     // Claim the chunk's ring slot and start its load; rows beyond the logical count become zeros.
     auto start = [&](int c) {
@@ -460,11 +417,11 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
         for (int r = 0; r < rpc; ++r) {
           char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
           if (P.num_in == 1) {
-            bulk_store(drow + static_cast<long long>(P.rank * hpr + u0) * 256, buf + r * chunk_row_bytes,
+            bulk_store(drow + sched::recv_column(P.rank, hpr, u0, 1, 0) * 2, buf + r * chunk_row_bytes,
                        chunk_row_bytes);
           } else {
             for (int u = 0; u < upp; ++u) {
-              const long long col = (static_cast<long long>(P.rank * hpr + u0 + u) * P.num_in + t) * 128;
+              const long long col = sched::recv_column(P.rank, hpr, u0 + u, P.num_in, t);
               bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
             }
           }
@@ -495,12 +452,8 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
   ring.parity = parity;
 }
 
-// Jobs of the first raster groups, which the GEMM cannot start without: every pusher warp of every
-// CTA works on them (as in fused_gemm_a2a_kernels.py:358-380). What follows is the steady phase.
 __device__ __forceinline__ long long first_phase_jobs(const GemmParams& P) {
-  const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
-  const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
-  return min(num_jobs, static_cast<long long>(min(2 * P.group_m, P.m_tiles)) * 2 * jobs_per_block);
+  return sched::first_phase_jobs(P.m_tiles, P.group_m, P.num_in, P.p, P.split);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -563,12 +516,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem
     const int col0 = pc * piece_cols;
     char* dst = nullptr;
     if (P.mode == kPush) {
-      const int unit = (b_row0 + col0) >> 7;  // 128-wide head tile in weight-row order
-      const int head = unit / P.segments, seg = unit - head * P.segments;
-      const int dest = head / P.heads_per_rank, within = head - dest * P.heads_per_rank;
-      dst = reinterpret_cast<char*>(P.peer_heads[seg][dest]) +
-            ((static_cast<long long>(P.rank) * P.head_rows + row) * P.head_pitch + within * 128 +
-             ((b_row0 + col0) & 127)) * 2;
+      const sched::PushRoute route = sched::push_route(b_row0 + col0, P.segments, P.heads_per_rank);
+      dst = reinterpret_cast<char*>(P.peer_heads[route.segment][route.dest]) +
+            sched::push_element(route, P.rank, P.head_rows, row, P.head_pitch) * 2;
     } else if (row < P.c_rows) {
       dst = static_cast<char*>(P.c) +
             (static_cast<long long>(row) * P.c_pitch + b_row0 + col0) * (bf16_out ? 2 : 4);

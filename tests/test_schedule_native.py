@@ -1,0 +1,239 @@
+"""The kernel's index arithmetic on the CPU. csrc/schedule.cuh holds the integer functions that the
+CUDA kernel, its launchers and nothing else use to decide which tile a CTA pair computes, which K
+steps a work unit covers, where a finished head tile goes on which peer, and which rows a pusher
+job moves. tests/native/schedule_host.cpp compiles the same header with g++; here every function is
+checked for the properties the kernel depends on (each tile, K step, job and byte exactly once; a
+persistent grid's stride schedule; both pusher schedules) and the routing is compared with the
+oracle's buffer layouts, for the benchmark geometries and a sweep of small ones.
+"""
+import ctypes
+import itertools
+import os
+import subprocess
+
+import pytest
+import torch
+
+from oracle.ulysses_oracle import UlyssesOracle
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+I = ctypes.c_int
+L = ctypes.c_longlong
+
+
+@pytest.fixture(scope='module')
+def sched(tmp_path_factory):
+    out = tmp_path_factory.mktemp('sched') / 'libsched.so'
+    subprocess.run(['g++', '-O1', '-std=c++17', '-shared', '-fPIC', '-Wall', '-Werror', '-x', 'c++',
+                    os.path.join(HERE, 'native', 'schedule_host.cpp'), '-o', str(out)], check=True)
+    lib = ctypes.CDLL(str(out))
+    for name in ('sched_push_element', 'sched_push_jobs_total', 'sched_first_phase_jobs', 'sched_recv_column'):
+        getattr(lib, name).restype = L
+    lib.sched_push_element.argtypes = [I, I, I, I, L, I, L]
+    lib.sched_decode_push_job.argtypes = [L, I, I, I, I, ctypes.POINTER(I)]
+    lib.sched_pick_k_splits.argtypes = [L, I, I, I]
+    return lib
+
+
+def tile_of(lib, m_tiles, n_tiles, group_m, t):
+    m, n = I(), I()
+    lib.sched_tile_coords(m_tiles, n_tiles, group_m, t, ctypes.byref(m), ctypes.byref(n))
+    return m.value, n.value
+
+
+def unit_of(lib, k_tiles, k_splits, total, u):
+    t, a, b = I(), I(), I()
+    lib.sched_unit_coords(k_tiles, k_splits, total, u, ctypes.byref(t), ctypes.byref(a), ctypes.byref(b))
+    return t.value, a.value, b.value
+
+
+def job_of(lib, job, num_in, p, split, rank):
+    out = (I * 5)()
+    lib.sched_decode_push_job(job, num_in, p, split, rank, out)
+    return tuple(out)     # mi, t, d, q, row0
+
+
+def chunking(lib, hpr, sub_rows, buffer_bytes=4096):
+    units, rows = I(), I()
+    lib.sched_push_chunking(hpr, sub_rows, buffer_bytes, ctypes.byref(units), ctypes.byref(rows))
+    return units.value, rows.value
+
+
+# ------------------------------------------------------------------------------------ tiles
+@pytest.mark.parametrize('m_tiles,n_tiles,group_m', [(64, 48, 16), (64, 16, 4), (48, 16, 8), (16, 16, 8), (512, 48, 16),
+                                                     (1, 1, 4), (5, 3, 4), (7, 2, 3), (9, 5, 1), (3, 7, 16)])
+def test_raster_visits_every_tile_once_and_groups_rows(sched, m_tiles, n_tiles, group_m):
+    total = m_tiles * n_tiles
+    seen = [tile_of(sched, m_tiles, n_tiles, group_m, t) for t in range(total)]
+    assert sorted(seen) == sorted(itertools.product(range(m_tiles), range(n_tiles)))
+    # a raster group never mixes row tiles of different groups, and group g comes before g + 1
+    groups = [m // group_m for m, _ in seen]
+    assert groups == sorted(groups)
+    # inside a group the row tile varies fastest: consecutive tiles share the weight tile
+    first_group = [pair for pair in seen if pair[0] < group_m]
+    rows = min(group_m, m_tiles)
+    assert first_group[:rows] == [(m, 0) for m in range(rows)]
+
+
+@pytest.mark.parametrize('pairs', [1, 7, 71, 74])
+@pytest.mark.parametrize('total,k_tiles,k_splits', [(256, 256, 1), (256, 2048, 2), (768, 2048, 2), (10, 257, 8),
+                                                    (3, 64, 2), (1, 96, 3)])
+def test_units_cover_every_k_step_of_every_tile_once(sched, pairs, total, k_tiles, k_splits):
+    """The persistent grid's stride schedule (pair, pair + pairs, ...) over tiles x shares: each
+    (tile, K step) belongs to exactly one unit, shares are contiguous, balanced and never empty."""
+    covered = {}
+    for pair in range(pairs):
+        for u in range(pair, total * k_splits, pairs):
+            t, kt0, kt1 = unit_of(sched, k_tiles, k_splits, total, u)
+            assert 0 <= t < total and 0 <= kt0 < kt1 <= k_tiles
+            assert abs((kt1 - kt0) - k_tiles / k_splits) < 1
+            for kt in range(kt0, kt1):
+                assert covered.setdefault((t, kt), u) == u
+    assert len(covered) == total * k_tiles
+
+
+def test_rotation_is_a_permutation_that_starts_ranks_on_different_peers(sched):
+    for n_tiles, p in ((48, 8), (16, 8), (16, 2), (12, 4), (3, 1)):
+        for rank in range(p):
+            rotate = rank * (n_tiles // p)
+            order = [sched.sched_rotated_n(n, rotate, n_tiles) for n in range(n_tiles)]
+            assert sorted(order) == list(range(n_tiles)) and order[0] == rotate
+
+
+def test_share_count_selection(sched):
+    pick = sched.sched_pick_k_splits
+    assert pick(256, 2048, 74, 0) == 2      # 4096x4096 gradient over 131072 tokens: 3.46 waves -> 6.92
+    assert pick(768, 2048, 74, 0) == 2      # 12288x4096: 10.4 waves -> 20.8
+    assert pick(3072, 64, 74, 0) == 1       # already 98.8 % efficient
+    assert pick(256, 63, 74, 0) == 1        # a share must keep 32 K steps
+    assert pick(1, 256, 74, 0) == 8         # a single tile: as many shares as allowed
+    assert pick(256, 2048, 74, 4) == 4 and pick(256, 100, 74, 4) == 3 and pick(256, 40, 74, 4) == 1
+    for tiles, k_tiles in itertools.product((1, 5, 74, 75, 256, 768, 1000), (32, 64, 100, 256, 4096)):
+        s = pick(tiles, k_tiles, 74, 0)
+        assert 1 <= s <= 8 and (s == 1 or k_tiles // s >= 32)
+
+
+# ------------------------------------------------------------------------------------ push routing
+@pytest.mark.parametrize('p,hidden,heads,segments', [(1, 512, 4, 3), (2, 512, 4, 3), (4, 1024, 8, 4), (8, 1024, 8, 3),
+                                                     (2, 512, 4, 1), (8, 1024, 8, 1)])
+def test_push_routing_matches_the_oracle_layout(sched, p, hidden, heads, segments):
+    """Every output column of every source rank goes where the oracle's head-side buffers have it.
+    The activations are made to encode (source rank, row, column) through an identity-like weight,
+    so a buffer element names the GEMM output element that must land there."""
+    tokens, capacity = 3, 256
+    hpr = heads // p
+    n = segments * hidden
+    oracle = UlyssesOracle(p, hidden, heads, max(segments, 1))
+    # y[r][row, col] = code(r, row, col): build expected buffers from the oracle's own routing
+    codes = [torch.arange(tokens * n, dtype=torch.float32).reshape(tokens, n) + 100000 * r for r in range(p)]
+    if segments > 1:
+        expected = [[torch.full((p * capacity, hidden // p), -1.0) for _ in range(segments)] for _ in range(p)]
+        for r in range(p):
+            y = codes[r].reshape(tokens, heads, segments, 128)
+            for dest in range(p):
+                for seg in range(segments):
+                    expected[dest][seg][r * capacity:r * capacity + tokens] = \
+                        y[:, dest * hpr:(dest + 1) * hpr, seg, :].reshape(tokens, hidden // p)
+    else:
+        expected = [[torch.full((p * capacity, hidden // p), -1.0)] for _ in range(p)]
+        for r in range(p):
+            for dest in range(p):
+                expected[dest][0][r * capacity:r * capacity + tokens] = \
+                    codes[r][:, dest * (hidden // p):(dest + 1) * (hidden // p)]
+    assert oracle.c == hidden // p
+    got = [[torch.full((p * capacity, hidden // p), -1.0) for _ in range(segments)] for _ in range(p)]
+    out = (I * 3)()
+    for r in range(p):
+        for col in range(n):
+            sched.sched_push_route(col, segments, hpr, out)
+            seg, dest, column = tuple(out)
+            for row in range(tokens):
+                element = sched.sched_push_element(col, segments, hpr, r, capacity, row, hidden // p)
+                assert element == (r * capacity + row) * (hidden // p) + column
+                got[dest][seg].view(-1)[element] = codes[r][row, col]
+    for dest in range(p):
+        for seg in range(segments):
+            assert torch.equal(got[dest][seg], expected[dest][seg]), (dest, seg)
+
+
+# ------------------------------------------------------------------------------------ pusher jobs
+@pytest.mark.parametrize('m_tiles,num_in,p,split,group_m', [(64, 3, 8, 2, 4), (64, 1, 8, 2, 4), (2, 3, 2, 4, 4),
+                                                            (5, 4, 4, 1, 1), (11, 1, 1, 8, 4), (1, 3, 8, 2, 4)])
+@pytest.mark.parametrize('grid,push_pairs', [(148, 0), (148, 4), (148, 73), (4, 1), (2, 0)])
+def test_both_pusher_schedules_run_every_job_once(sched, m_tiles, num_in, p, split, group_m, grid, push_pairs):
+    """All CTAs x 4 warps take the first two raster groups; then either `push_warps` warps of every
+    CTA or all ten warps of the pushing-only CTAs take the rest. Every job exactly once, for any rank."""
+    total = sched.sched_push_jobs_total(m_tiles, num_in, p, split)
+    first = sched.sched_first_phase_jobs(m_tiles, group_m, num_in, p, split)
+    assert total == m_tiles * 2 * num_in * p * split
+    assert first == min(total, min(2 * group_m, m_tiles) * 2 * num_in * p * split)
+    runs = [0] * total
+    for cta in range(grid):
+        for warp in range(4):
+            for job in range(cta * 4 + warp, first, grid * 4):
+                runs[job] += 1
+    if push_pairs == 0:
+        for push_warps in (1, 2, 4):
+            again = list(runs)
+            for cta in range(grid):
+                for warp in range(push_warps):
+                    for job in range(first + cta * push_warps + warp, total, grid * push_warps):
+                        again[job] += 1
+            assert again == [1] * total
+    else:
+        gemm_pairs = grid // 2 - push_pairs
+        for cta in range(2 * gemm_pairs, grid):
+            for warp in range(10):
+                for job in range(first + (cta - 2 * gemm_pairs) * 10 + warp, total, 2 * push_pairs * 10):
+                    runs[job] += 1
+        assert runs == [1] * total
+    # decoding: a bijection onto (row block, segment, destination, sub-block), destinations rotated by rank
+    for rank in range(p):
+        decoded = [job_of(sched, job, num_in, p, split, rank) for job in range(total)]
+        assert sorted(d[:4] for d in decoded) == sorted(itertools.product(range(m_tiles * 2), range(num_in), range(p), range(split)))
+        assert all(row0 == mi * 128 + q * (128 // split) for mi, _, _, q, row0 in decoded)
+        assert decoded[0][2] == rank and [d[0] for d in decoded] == sorted(d[0] for d in decoded)
+
+
+@pytest.mark.parametrize('hpr,num_in,split', [(4, 3, 2), (4, 1, 2), (16, 3, 4), (32, 1, 8), (1, 4, 1), (3, 3, 1), (20, 1, 4),
+                                              (17, 1, 4)])
+def test_chunks_move_every_byte_of_a_job_once_and_zero_the_missing_rows(sched, hpr, num_in, split):
+    sub_rows = 128 // split
+    units, rows = chunking(sched, hpr, sub_rows)
+    assert units * rows * 256 <= 4096 and hpr % units == 0 and sub_rows % rows == 0
+    assert rows == 1 or units == hpr
+    count = sched.sched_push_chunks_per_job(hpr, units, rows, sub_rows)
+    out = (I * 3)()
+    for src_rows, row0 in ((10 ** 6, 0), (sub_rows + 3, sub_rows), (5, 0), (128, 128)):
+        moved = torch.zeros(sub_rows, hpr, dtype=torch.int32)
+        zeros = torch.zeros(sub_rows, hpr, dtype=torch.int32)
+        for c in range(count):
+            sched.sched_push_chunk(c, hpr, units, rows, src_rows, row0, out)
+            r0, u0, valid = tuple(out)
+            assert 0 <= valid <= rows
+            moved[r0:r0 + rows, u0:u0 + units] += 1
+            zeros[r0 + valid:r0 + rows, u0:u0 + units] += 1
+        assert bool((moved == 1).all())
+        exists = (torch.arange(sub_rows) + row0 < src_rows).int().view(-1, 1).expand(-1, hpr)
+        assert torch.equal(zeros, 1 - exists)
+
+
+@pytest.mark.parametrize('p,hidden,heads,num_in', [(2, 512, 4, 3), (4, 1024, 8, 4), (8, 1024, 8, 3), (8, 1024, 8, 1)])
+def test_receive_columns_match_the_oracle_layout(sched, p, hidden, heads, num_in):
+    """Where the pushers of every rank put each head unit in a destination's receive buffer, against
+    the oracle's receive buffers built from tensors that encode (rank, segment, row, column)."""
+    tokens, hpr = 2, heads // p
+    oracle = UlyssesOracle(p, hidden, heads, max(num_in, 1))
+    sources = [tuple(torch.arange(p * tokens * hpr * 128, dtype=torch.float32).reshape(p * tokens, hpr, 128)
+                     + 1e6 * r + 1e5 * t for t in range(num_in)) for r in range(p)]
+    for dest in range(p):
+        want = (oracle.qkv_recv_buffer(sources, dest) if num_in > 1
+                else oracle.out_recv_buffer([s[0] for s in sources], dest))
+        got = torch.full_like(want, -1.0)
+        for r in range(p):
+            for t in range(num_in):
+                block = sources[r][t][dest * tokens:(dest + 1) * tokens]        # rows this rank sends to dest
+                for unit in range(hpr):
+                    column = sched.sched_recv_column(r, hpr, unit, num_in, t)
+                    got[:, column:column + 128] = block[:, unit]
+        assert torch.equal(got, want)
