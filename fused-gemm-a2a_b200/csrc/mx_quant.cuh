@@ -4,27 +4,18 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include "mx_rule.cuh"
 
 namespace fga {
 
+// The scale rule and the scale-byte layout are plain integer functions (mx_rule.cuh), compiled for
+// the host as well so that the CPU tests can sweep them against the oracle.
 __device__ __forceinline__ void mx_scale(float peak, int& exponent, float& inv_scale) {
-  exponent = 0;
-  if (peak > 0.f) {
-    const int bits = __float_as_int(peak);
-    exponent = (bits >> 23) - 135;
-    if ((bits & 0x7fffff) > 0x600000) exponent += 1;
-    exponent = max(-126, min(127, exponent));
-  }
-  inv_scale = __int_as_float((127 - exponent) << 23);
-  if (peak == __int_as_float(0x7f800000)) {
-    exponent = 128;
-    inv_scale = 0.f;
-  }
+  rule::mx_scale(peak, exponent, inv_scale);
 }
 
 __device__ __forceinline__ long long mx_scale_offset(long long row, int group, int groups) {
-  return ((row / 128) * (groups / 4) + group / 4) * 512 + (row % 32) * 16 + (row % 128 / 32) * 4 +
-         group % 4;
+  return rule::mx_scale_offset(row, group, groups);
 }
 
 __device__ __forceinline__ uint16_t to_e4m3x2(float lo, float hi) {

@@ -2,6 +2,7 @@
 // entry points over the same inline functions the CUDA kernel and its launchers compile.
 // Built by tests/test_schedule_native.py with g++; not part of libfga.so.
 #include "../../fused-gemm-a2a_b200/csrc/schedule.cuh"
+#include "../../fused-gemm-a2a_b200/csrc/mx_rule.cuh"
 
 using namespace fga::sched;
 
@@ -70,6 +71,20 @@ long long sched_recv_column(int rank, int heads_per_rank, int unit, int num_in, 
 
 int sched_pick_k_splits(long long tiles, int k_tiles, int pairs, int forced) {
   return pick_k_splits(tiles, k_tiles, pairs, forced);
+}
+
+// MXFP8 scale rule on `count` FP32 bit patterns: exponents[i] (128 = the NaN scale) and the bit
+// patterns of the multipliers.
+void rule_mx_scale(const int* peak_bits, int count, int* exponents, int* multiplier_bits) {
+  for (int i = 0; i < count; ++i) {
+    float inv;
+    fga::rule::mx_scale(fga::rule::bits_float(peak_bits[i]), exponents[i], inv);
+    multiplier_bits[i] = fga::rule::float_bits(inv);
+  }
+}
+
+long long rule_mx_scale_offset(long long row, int group, int groups) {
+  return fga::rule::mx_scale_offset(row, group, groups);
 }
 
 }  // extern "C"

@@ -14,6 +14,7 @@ import subprocess
 import pytest
 import torch
 
+from oracle import mxfp8_oracle
 from oracle.ulysses_oracle import UlyssesOracle
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -32,6 +33,8 @@ def sched(tmp_path_factory):
     lib.sched_push_element.argtypes = [I, I, I, I, L, I, L]
     lib.sched_decode_push_job.argtypes = [L, I, I, I, I, ctypes.POINTER(I)]
     lib.sched_pick_k_splits.argtypes = [L, I, I, I]
+    lib.rule_mx_scale_offset.restype = L
+    lib.rule_mx_scale_offset.argtypes = [L, I, I]
     return lib
 
 
@@ -114,42 +117,49 @@ def test_share_count_selection(sched):
 
 
 # ------------------------------------------------------------------------------------ push routing
+class _CodedOracle(UlyssesOracle):
+    """The oracle with the QKV GEMM replaced by a table: rank r's projection output is codes[r], so
+    that its head-side buffers show, element by element, which output element belongs where."""
+
+    def __init__(self, codes, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.codes = codes
+
+    def qkv_sequence_side(self, x):
+        table = self.codes[int(x[0, 0])]
+        out = torch.zeros(x.shape[0], table.shape[1])
+        out[:table.shape[0]] = table
+        return out
+
+
 @pytest.mark.parametrize('p,hidden,heads,segments', [(1, 512, 4, 3), (2, 512, 4, 3), (4, 1024, 8, 4), (8, 1024, 8, 3),
                                                      (2, 512, 4, 1), (8, 1024, 8, 1)])
 def test_push_routing_matches_the_oracle_layout(sched, p, hidden, heads, segments):
-    """Every output column of every source rank goes where the oracle's head-side buffers have it.
-    The activations are made to encode (source rank, row, column) through an identity-like weight,
-    so a buffer element names the GEMM output element that must land there."""
+    """Every output element of every source rank lands where the oracle's head-side buffers have it.
+    The GEMM output of rank r is a table of distinct codes (through a stand-in for the QKV GEMM, or an
+    identity weight for the output-projection dgrad), so equality of the buffers is equality of the
+    routing."""
     tokens, capacity = 3, 256
-    hpr = heads // p
+    hpr, width = heads // p, hidden // p
     n = segments * hidden
-    oracle = UlyssesOracle(p, hidden, heads, max(segments, 1))
-    # y[r][row, col] = code(r, row, col): build expected buffers from the oracle's own routing
-    codes = [torch.arange(tokens * n, dtype=torch.float32).reshape(tokens, n) + 100000 * r for r in range(p)]
+    codes = [torch.arange(1, tokens * n + 1, dtype=torch.float32).reshape(tokens, n) + 100000 * r for r in range(p)]
     if segments > 1:
-        expected = [[torch.full((p * capacity, hidden // p), -1.0) for _ in range(segments)] for _ in range(p)]
-        for r in range(p):
-            y = codes[r].reshape(tokens, heads, segments, 128)
-            for dest in range(p):
-                for seg in range(segments):
-                    expected[dest][seg][r * capacity:r * capacity + tokens] = \
-                        y[:, dest * hpr:(dest + 1) * hpr, seg, :].reshape(tokens, hidden // p)
+        oracle = _CodedOracle(codes, p, hidden, heads, segments, dtype=torch.float32)
+        xs = [torch.full((tokens, hidden), float(r)) for r in range(p)]
+        expected = oracle.qkv_heads_buffers(xs, capacity)
     else:
-        expected = [[torch.full((p * capacity, hidden // p), -1.0)] for _ in range(p)]
-        for r in range(p):
-            for dest in range(p):
-                expected[dest][0][r * capacity:r * capacity + tokens] = \
-                    codes[r][:, dest * (hidden // p):(dest + 1) * (hidden // p)]
-    assert oracle.c == hidden // p
-    got = [[torch.full((p * capacity, hidden // p), -1.0) for _ in range(segments)] for _ in range(p)]
+        oracle = UlyssesOracle(p, hidden, heads, 1, weight_out=torch.eye(hidden), dtype=torch.float32)
+        expected = [[buffer] for buffer in oracle.out_dhead_buffers(codes, capacity)]
+    got = [[torch.zeros(p * capacity, width) for _ in range(segments)] for _ in range(p)]
     out = (I * 3)()
     for r in range(p):
         for col in range(n):
             sched.sched_push_route(col, segments, hpr, out)
             seg, dest, column = tuple(out)
+            assert 0 <= seg < segments and 0 <= dest < p and 0 <= column < width
             for row in range(tokens):
-                element = sched.sched_push_element(col, segments, hpr, r, capacity, row, hidden // p)
-                assert element == (r * capacity + row) * (hidden // p) + column
+                element = sched.sched_push_element(col, segments, hpr, r, capacity, row, width)
+                assert element == (r * capacity + row) * width + column
                 got[dest][seg].view(-1)[element] = codes[r][row, col]
     for dest in range(p):
         for seg in range(segments):
@@ -237,3 +247,38 @@ def test_receive_columns_match_the_oracle_layout(sched, p, hidden, heads, num_in
                     column = sched.sched_recv_column(r, hpr, unit, num_in, t)
                     got[:, column:column + 128] = block[:, unit]
         assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------------------------ MXFP8 rule
+def test_scale_rule_equals_the_oracle_on_every_bf16_magnitude_and_around_every_threshold(sched):
+    """The CUDA quantizer's scale rule (csrc/mx_rule.cuh, compiled here for the host) against the
+    oracle, which is pinned by the reference tests' known answers: all BF16 magnitudes including
+    zero, subnormals and +Inf, and for every binade the FP32 values at and next to the rounding
+    threshold (mantissa 0x600000) and the binade's ends."""
+    import numpy as np
+    bf16 = np.arange(0x0000, 0x7f81, dtype=np.int64) << 16
+    exponents = np.arange(0, 255, dtype=np.int64) << 23
+    around = np.concatenate([exponents + m for m in (0, 1, 0x5fffff, 0x600000, 0x600001, 0x7fffff)])
+    patterns = np.concatenate([bf16, around]).astype(np.int32)
+    got_e = np.zeros(len(patterns), dtype=np.int32)
+    got_m = np.zeros(len(patterns), dtype=np.int32)
+    sched.rule_mx_scale(patterns.ctypes.data_as(ctypes.POINTER(I)), len(patterns),
+                        got_e.ctypes.data_as(ctypes.POINTER(I)), got_m.ctypes.data_as(ctypes.POINTER(I)))
+    want_e, want_m = mxfp8_oracle.mx_scale(patterns.view(np.float32))
+    assert np.array_equal(got_e, want_e)
+    assert np.array_equal(got_m, want_m.view(np.int32))
+    assert got_e[0] == 0 and got_m[0] == 0x3f800000                  # zero group: scale 1
+    assert got_e[0x7f80] == 128 and got_m[0x7f80] == 0               # +Inf group: NaN scale, multiplier 0
+    assert got_e.min() == -126 and got_e[:0x7f80].max() == 120      # clamped below; the largest finite BF16 needs 2^120
+
+
+def test_scale_bytes_fill_the_tcgen05_blocks_exactly(sched):
+    import numpy as np
+    for rows, groups in ((256, 4), (256, 16), (512, 40), (1024, 8)):
+        offsets = np.array([[sched.rule_mx_scale_offset(r, g, groups) for g in range(groups)] for r in range(rows)])
+        want = mxfp8_oracle.scale_offset(np.arange(rows)[:, None], np.arange(groups)[None, :], groups)
+        assert np.array_equal(offsets, want)
+        assert sorted(offsets.ravel().tolist()) == list(range(rows * groups))     # a bijection onto the buffer
+        # one 512-byte block per (128 rows, 4 groups); the four groups of a row are adjacent bytes
+        assert np.array_equal(offsets // 512, (np.arange(rows)[:, None] // 128) * (groups // 4) + np.arange(groups)[None, :] // 4)
+        assert np.array_equal(offsets[:, 1] - offsets[:, 0], np.ones(rows, dtype=offsets.dtype))
