@@ -262,7 +262,10 @@ class _Comm:
               buffers, peer counters]); c [rows, N] is the local output.
         b is [N, K] or, with b_is_kn, [K, N]."""
         if scales:
-            raise NotImplementedError('The block-scaled MXFP8 GEMM is not part of this build yet')
+            # The reference passes quantized operands and their scales through this method. Here the
+            # MXFP8 launches are issued by the workspace view (run_push / run_recv), which owns the
+            # quantized copies; this entry point takes BF16 operands only.
+            raise NotImplementedError('_Comm.gemm takes BF16 operands; MXFP8 launches go through the workspace view')
         if mode not in ('push', 'recv'):
             raise ValueError('GEMM mode must be push/recv and tile N must divide output width')
         if not all(t.is_contiguous() for t in (a, b, c)):
