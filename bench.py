@@ -38,7 +38,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 LINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool (900 nominal)
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per FLOP of the GEMM kernel, from the ncu
 # captures of `--kernel-case gemm_nt` (670.4 MB) and `--kernel-case wgrad` (1296.8 MB), both
-# 824.6 GFLOP launches at 8192 tokens (profiles/ulysses_gemm_kernel_bf16_*.md). The benchmark's
+# 824.6 GFLOP launches at 8192 tokens (summaries of both captures are kept under profiles/). The benchmark's
 # launches are too large to capture; traffic grows with the rows, so it is scaled by the FLOPs.
 DRAM_BYTES_PER_FLOP = dict(gemm=670.4e6 / 824.6e9, wgrad=1296.8e6 / 824.6e9)
 

@@ -2,7 +2,7 @@
 
 Run in a container that has the reference tree (it cannot travel to the GPU box):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of the reference project>
 
 Spawns CPU ranks (gloo, 127.0.0.1), imports benchmark/reference.py from the reference tree, runs
 UlyssesQKVProjection and UlyssesOutputProjection forward + backward and writes
@@ -140,7 +140,9 @@ def collect(world, reference_root, port):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument('--reference', default='/root/reference')
+    ap.add_argument('--reference', default=os.environ.get(
+        'FGA_REFERENCE_ROOT', os.path.join(os.path.expanduser('~'), 'reference')),
+        help='checkout of the reference project (default: $FGA_REFERENCE_ROOT, else ~/reference)')
     args = ap.parse_args()
     for world, port in ((2, 29611), (4, 29612)):
         per_rank = collect(world, args.reference, port)
