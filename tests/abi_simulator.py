@@ -14,7 +14,10 @@ on host memory, following the header's contract (not the CUDA sources):
     between its pushing half and its computing half (each simulated "kernel" runs to completion
     on the host, so this is the only point where ranks must meet);
   * GEMMs accumulate in FP32 from the BF16 values and round once, the arithmetic of the oracle.
-BF16 only; the MXFP8 launch plan is covered by the call traces (tests/host_trace.py).
+  * MXFP8: the quantizer wrapper remembers which BF16 matrix every quantized operand came from, and
+    the block-scaled GEMMs multiply the exact dequantized values of both operands, each quantized
+    along the GEMM's reduction axis (oracle/mxfp8_oracle.py); the receive GEMM quantizes what is in
+    the receive buffer once all arrivals are in, as the quantizer warps do.
 """
 import ctypes
 import os
@@ -42,6 +45,16 @@ def table(address, entries):
     return list((ctypes.c_int64 * entries).from_address(int(address)))
 
 
+def bf16_bits(t):
+    return t.contiguous().view(torch.int16).numpy().view('uint16')
+
+
+def mx_product(a, b):
+    """a [M, K] x b [N, K]^T with both operands quantized to MXFP8 along K, exact products, FP32 result."""
+    from oracle import mxfp8_oracle
+    return torch.from_numpy(mxfp8_oracle.mx_matmul(bf16_bits(a), bf16_bits(b))).float()
+
+
 class SimulatedLibrary:
     def __init__(self, tag):
         self.tag = tag                    # unique per test run: names of the shared segments
@@ -49,6 +62,13 @@ class SimulatedLibrary:
         self.segments = []                # SharedMemory objects this process created or opened
         self.created = []
         self.launches = 0
+        self.quantized = []               # (payload tensor, BF16 matrix it was quantized from), kept alive
+
+    def source_of(self, address):
+        for payload, source in reversed(self.quantized):
+            if payload.data_ptr() == address:
+                return source
+        raise KeyError('operand was not produced by the quantizer wrapper')
 
     def fga_last_error(self):
         return b'simulated library: a receive row block did not collect all of its arrivals'
@@ -93,6 +113,17 @@ class SimulatedLibrary:
                 pass
 
     # ---- fused GEMMs (contract: include/fga.h)
+    def _route_push(self, product, a_rows, segments, n_segment, tables, head_rows, rank, p):
+        """Store a [a_rows, segments*n_segment] BF16 result unit by unit (128 columns = one head of one
+        segment) into the head-side buffers of the peers that own the heads."""
+        heads_per_rank = n_segment // p // 128
+        for unit in range(segments * n_segment // 128):
+            head, segment = (unit // segments, unit % segments) if segments > 1 else (unit, 0)
+            dest, within = head // heads_per_rank, head % heads_per_rank
+            target = matrix(table(tables[segment], p)[dest], p * head_rows, n_segment // p)
+            target[rank * head_rows:rank * head_rows + a_rows, within * 128:(within + 1) * 128] = \
+                product[:, unit * 128:(unit + 1) * 128]
+
     def fga_gemm_push(self, a, m, k, a_rows, b, b_is_kn, bias, segments, n_segment, tables, head_rows,
                       rank, p, status, timeout, stream):
         self.launches += 1
@@ -103,19 +134,24 @@ class SimulatedLibrary:
         product = padded.float() @ weight.float().t()
         if bias:
             product = product + matrix(bias, 1, n).float()
-        product = product.to(BF16)
-        heads_per_rank = n_segment // p // 128
-        for unit in range(n // 128):                       # one 128-column (head, segment) unit at a time
-            head, segment = (unit // segments, unit % segments) if segments > 1 else (unit, 0)
-            dest, within = head // heads_per_rank, head % heads_per_rank
-            target = matrix(table(tables[segment], p)[dest], p * head_rows, n_segment // p)
-            target[rank * head_rows:rank * head_rows + a_rows, within * 128:(within + 1) * 128] = \
-                product[:, unit * 128:(unit + 1) * 128]
+        self._route_push(product.to(BF16), a_rows, segments, n_segment, tables, head_rows, rank, p)
         return 0
 
-    def fga_gemm_recv(self, recv, recv_rows, k, b, b_is_kn, n, c, peer_recv, peer_counters, counters,
-                      srcs, num_in, src_rows, split, rank, p, roles, epoch, progress, status, timeout, stream):
+    def fga_gemm_push_mx(self, aq, sfa, a_rows_padded, kp, a_rows, bq, sfb, b_rows_padded, bias, segments,
+                         n_segment, tables, head_rows, rank, p, status, timeout, stream):
         self.launches += 1
+        n = segments * n_segment
+        activations, weight = self.source_of(aq), self.source_of(bq)     # [m, k] and [n, k]
+        assert weight.shape[0] == n and activations.shape[1] == weight.shape[1]
+        assert a_rows_padded >= a_rows >= activations.shape[0] and b_rows_padded >= n and kp >= weight.shape[1]
+        product = torch.zeros(a_rows, n)
+        product[:activations.shape[0]] = mx_product(activations, weight)
+        if bias:
+            product = product + matrix(bias, 1, n).float()
+        self._route_push(product.to(BF16), a_rows, segments, n_segment, tables, head_rows, rank, p)
+        return 0
+
+    def _push_inputs(self, recv_rows, k, peer_recv, peer_counters, srcs, num_in, src_rows, split, rank, p, roles):
         heads_per_rank = k // (p * num_in * 128)
         for turn in range(p if roles & 2 else 0):
             # One rank pushes at a time: the counter increments below are plain read-modify-writes
@@ -137,12 +173,43 @@ class SimulatedLibrary:
             dist.barrier()                     # after the last turn: every row block has all its arrivals
         if not roles & 2:
             dist.barrier()
+
+    def _arrived(self, counters, recv_rows, expected, roles):
+        own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
+        return not roles & 2 or bool((own == expected).all())
+
+    def fga_gemm_recv(self, recv, recv_rows, k, b, b_is_kn, n, c, peer_recv, peer_counters, counters,
+                      srcs, num_in, src_rows, split, rank, p, roles, epoch, progress, status, timeout, stream):
+        self.launches += 1
+        self._push_inputs(recv_rows, k, peer_recv, peer_counters, srcs, num_in, src_rows, split, rank, p, roles)
         if roles & 1:
-            own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
-            if roles & 2 and not bool((own == p * num_in * split).all()):
+            if not self._arrived(counters, recv_rows, p * num_in * split, roles):
                 return -2
             weight = matrix(b, k, n).t() if b_is_kn else matrix(b, n, k)
             matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ weight.float().t()).to(BF16)
+        return 0
+
+    def fga_gemm_recv_mx(self, recv, mx_recv, mx_scale, recv_rows, k, bq, sfb, b_rows_padded, b_kp, n, c,
+                         peer_recv, peer_counters, counters, srcs, num_in, src_rows, split, rank, p, roles,
+                         epoch, progress, status, timeout, stream):
+        from oracle import mxfp8_oracle
+        self.launches += 1
+        self._push_inputs(recv_rows, k, peer_recv, peer_counters, srcs, num_in, src_rows, split, rank, p, roles)
+        if roles & 1:
+            if not self._arrived(counters, recv_rows, p * num_in * split, roles):
+                return -2
+            received = matrix(recv, recv_rows, k)
+            # what the quantizer warps leave behind: the E4M3 copy and its scales (K padded to 128)
+            payload, scales = mxfp8_oracle.quantize(bf16_bits(received), k_multiple=128)
+            torch.frombuffer(_bytes_at(mx_recv, recv_rows * k), dtype=torch.uint8).copy_(
+                torch.from_numpy(payload[:recv_rows, :k].copy()).reshape(-1))
+            torch.frombuffer(_bytes_at(mx_scale, recv_rows * k // 32), dtype=torch.uint8).copy_(
+                torch.from_numpy(scales[:recv_rows * k // 32].copy()))
+            own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
+            own += 16                      # the quantizer warps' completions, 8 rows per job
+            weight = self.source_of(bq)
+            assert weight.shape == (n, k) and b_rows_padded >= n and b_kp >= k
+            matrix(c, recv_rows, n)[:] = mx_product(received, weight).to(BF16)
         return 0
 
 
@@ -151,7 +218,7 @@ def install(fused, tag):
     import _fga_native
     from oracle.ulysses_oracle import reduce_bias_grad_ref, resize_rank_rows_ref
     sim = SimulatedLibrary(tag)
-    names = ('device_barrier', 'resize_rank_rows', 'reduce_bias_grad', 'bf16_wgrad')
+    names = ('device_barrier', 'resize_rank_rows', 'reduce_bias_grad', 'bf16_wgrad', 'mxfp8_quantize', 'mxfp8_wgrad')
     saved = {name: getattr(fused, name) for name in names}
     saved.update(lib=_fga_native.lib, torch=fused.torch, wrap=fused._wrap)
     _fga_native.lib = lambda: sim
@@ -181,7 +248,21 @@ def install(fused, tag):
         out.copy_((out.float() + product) if accumulate else product)
         return out
 
-    for fn in (device_barrier, resize_rank_rows, reduce_bias_grad, bf16_wgrad):
+    def mxfp8_quantize(a, *, k_multiple=256):
+        sim.launches += 1
+        rows, k = a.shape
+        rp, kp = -(-rows // 256) * 256, -(-k // k_multiple) * k_multiple
+        payload = torch.zeros(rp, kp, dtype=torch.float8_e4m3fn)
+        sim.quantized.append((payload, a.detach().contiguous().clone()))     # the logical [rows, k] matrix
+        return payload, torch.zeros(rp * kp // 32, dtype=torch.uint8)
+
+    def mxfp8_wgrad(dy, x, out, *, accumulate=False):
+        sim.launches += 3                  # two transposing quantizer passes and the GEMM
+        product = mx_product(dy.t(), x.t())           # both operands quantized along the token axis
+        out.copy_((out.float() + product) if accumulate else product)
+        return out
+
+    for fn in (device_barrier, resize_rank_rows, reduce_bias_grad, bf16_wgrad, mxfp8_quantize, mxfp8_wgrad):
         setattr(fused, fn.__name__, fn)
 
     def undo(meet=True):

@@ -19,9 +19,12 @@ import torch.multiprocessing as mp
 HERE = os.path.dirname(os.path.abspath(__file__))
 BF = torch.bfloat16
 
-CASES = (dict(gate=False, bias=False, bias_in_gemm=False, main_grad=False),
-         dict(gate=True, bias=True, bias_in_gemm=False, main_grad=False),
-         dict(gate=False, bias=True, bias_in_gemm=True, main_grad=True))
+CASES = (dict(gate=False, bias=False, bias_in_gemm=False, main_grad=False, precision='bf16'),
+         dict(gate=True, bias=True, bias_in_gemm=False, main_grad=False, precision='bf16'),
+         dict(gate=False, bias=True, bias_in_gemm=True, main_grad=True, precision='bf16'),
+         dict(gate=False, bias=False, bias_in_gemm=False, main_grad=False, precision='mxfp8'),
+         dict(gate=True, bias=True, bias_in_gemm=False, main_grad=True, precision='mxfp8'),
+         dict(gate=False, bias=True, bias_in_gemm=True, main_grad=False, precision='mxfp8'))
 
 
 def close(actual, expected, what):
@@ -62,13 +65,25 @@ def everyone(value):
 def run_rank(hidden, heads, capacity_tokens, token_counts):
     import abi_simulator
     import fused_gemm_a2a as fused
+    import numpy as np
+    from oracle import mxfp8_oracle, ulysses_oracle
     from oracle.ulysses_oracle import UlyssesOracle
     p, rank = dist.get_world_size(), dist.get_rank()
+    plain_mm = ulysses_oracle._mm
+
+    def mx_mm(a, b, acc_dtype):
+        """The oracle's GEMM with both operands quantized to MXFP8 along the reduction axis."""
+        return abi_simulator.mx_product(a.to(BF), b.t().to(BF)).to(acc_dtype)
+
     d = hidden // heads
     sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
     completed = False
     try:
         for case in CASES:
+            quantized = case['precision'] == 'mxfp8'
+            if quantized and p > 2 and case['gate']:
+                continue      # the numpy MXFP8 oracle is slow and every rank evaluates it for all ranks
+            ulysses_oracle._mm = mx_mm if quantized else plain_mm      # every GEMM of the oracle follows the precision
             segments = 4 if case['gate'] else 3
             g = torch.Generator().manual_seed(4321)            # parameters: the same on every rank
             wq = (torch.randn(segments * hidden, hidden, generator=g) / 32).to(BF)
@@ -84,13 +99,14 @@ def run_rank(hidden, heads, capacity_tokens, token_counts):
                     if param is not None:
                         start[name] = torch.randn(param.shape, generator=g)
                         param.main_grad = start[name].clone()
-            ws = fused.FusedGemmA2AWorkspace(hidden, heads, capacity_tokens, gate=case['gate'])
+            ws = fused.FusedGemmA2AWorkspace(hidden, heads, capacity_tokens, gate=case['gate'],
+                                             precision=case['precision'])
             qkv = fused.FusedQKVProjection(hidden, heads, weight=params['wq'], bias=params['bq'], gate=case['gate'],
                                            bias_in_gemm=case['bias_in_gemm'])
             proj = fused.FusedOutputProjection(hidden, heads, weight=params['wo'], bias=params['bo'])
             oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, bias_in_gemm=case['bias_in_gemm'])
             accumulated = {name: torch.zeros_like(t) for name, t in start.items()}
-            for tokens in token_counts:
+            for tokens in (token_counts[1:2] if quantized and p > 2 else token_counts):
                 g = torch.Generator().manual_seed(1000 * tokens + rank)
                 x = torch.randn(tokens, hidden, generator=g).to(BF).requires_grad_()
                 grads = [torch.randn(p * tokens, heads // p, d, generator=g).to(BF) for _ in range(segments)]
@@ -106,7 +122,12 @@ def run_rank(hidden, heads, capacity_tokens, token_counts):
                 got = torch.autograd.grad(outs, [x, params['wq']] + ([params['bq']] if case['bias'] else []), grads)
                 all_grads = everyone(tuple(grads))
                 same(view.recv, oracle.qkv_recv_buffer(all_grads, rank, cap), 'QKV dgrad transport')
-                assert view.counters.tolist() == [p * segments * fused._Comm.push_split(view.recv, segments, p)] * (cap // 128)
+                arrivals = p * segments * fused._Comm.push_split(view.recv, segments, p)
+                assert view.counters.tolist() == [arrivals + (16 if quantized else 0)] * (cap // 128)
+                if quantized:     # the receive-side quantizer's copy is the standalone quantizer's output
+                    payload, scales = mxfp8_oracle.quantize(abi_simulator.bf16_bits(view.recv), k_multiple=128)
+                    assert np.array_equal(view.mx_recv.view(torch.uint8).numpy(), payload[:cap])
+                    assert np.array_equal(view.mx_scale.numpy(), scales[:view.mx_scale.numel()])
                 for name, t, want in zip('qkvg', outs, oracle.qkv_forward(xs)[rank]):
                     close(t, want, f'{name} tokens={tokens}')
                     assert t.shape == (p * tokens, heads // p, d)
@@ -141,6 +162,7 @@ def run_rank(hidden, heads, capacity_tokens, token_counts):
         completed = True
         return sim.launches
     finally:
+        ulysses_oracle._mm = plain_mm
         undo(meet=completed)     # after a failure the peers are not at the same point: do not wait for them
 
 
@@ -181,5 +203,6 @@ def test_modules_on_simulated_ranks_match_the_oracle(world):
             if proc.is_alive():
                 proc.terminate()
     for rank, verdict, detail in sorted(results):
-        # 3 cases x 3 token counts x (6 barriers + 4 GEMMs + 2 weight gradients + 2 row copies [+ bias reductions])
-        assert detail >= 3 * 3 * 14
+        # at least 3 BF16 cases x 3 token counts x (6 barriers + 4 GEMMs + 2 weight gradients + 2 row copies)
+        # plus the MXFP8 cases
+        assert detail > 3 * 3 * 14
