@@ -51,3 +51,63 @@ def test_no_tma_load_fans_out_across_the_cluster():
         for line in open(os.path.join(csrc, name)):
             if needle in line:
                 assert 'cp.async' not in line, f'{name}: {line.strip()}'
+
+
+def _prototypes():
+    """name -> (return type, [parameter declarations]) for every function declared in fga.h."""
+    text = open(os.path.join(ROOT, 'include', 'fga.h')).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    text = re.sub(r'#.*', '', text)
+    found = {}
+    for ret, name, params in re.findall(r'([\w\s\*]+?)\b(fga_\w+)\s*\(([^)]*)\)\s*;', text):
+        params = [p.strip() for p in params.split(',')] if params.strip() not in ('', 'void') else []
+        found[name] = (' '.join(ret.split()), params)
+    return found
+
+
+def test_ctypes_signatures_match_the_header():
+    """Every binding in _fga_native.py has the header's parameter count, a pointer type exactly where
+    the header has a pointer or array, and the header's integer width elsewhere."""
+    import ctypes
+    lib = _fga_native.lib()
+    scalars = {'int': ctypes.c_int, 'int64_t': ctypes.c_int64, 'uint64_t': ctypes.c_uint64, 'size_t': ctypes.c_size_t}
+    pointers = (ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p))
+    returns = {'int': ctypes.c_int, 'int64_t': ctypes.c_int64, 'uint64_t': ctypes.c_uint64,
+               'const char*': ctypes.c_char_p, 'const char *': ctypes.c_char_p}
+    prototypes = _prototypes()
+    assert set(prototypes) == set(_fga_native.EXPORTS)
+    for name, (ret, params) in prototypes.items():
+        fn = getattr(lib, name)
+        assert fn.restype is returns[ret], f'{name}: return type {ret}'
+        argtypes = fn.argtypes or []
+        if not params:
+            assert not argtypes, name
+            continue
+        assert len(argtypes) == len(params), f'{name}: {len(argtypes)} bound, {len(params)} declared'
+        for bound, declared in zip(argtypes, params):
+            if '*' in declared or '[' in declared:
+                assert bound in pointers, f'{name}: `{declared}` bound as {bound}'
+            else:
+                base = declared.replace('const ', '').split()[0]
+                assert bound is scalars[base], f'{name}: `{declared}` bound as {bound}'
+
+
+def test_cpu_stand_ins_take_the_header_parameters():
+    """The recorder and the simulator used by the host-layer tests restate entry points of the
+    header; their parameter lists must follow it (a drifted stand-in would test a different ABI)."""
+    import inspect
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
+    import abi_simulator
+    import host_trace
+    prototypes = _prototypes()
+    checked = 0
+    for cls in (host_trace.FakeLib, abi_simulator.SimulatedLibrary):
+        for name, member in inspect.getmembers(cls, inspect.isfunction):
+            if not name.startswith('fga_') or name == 'fga_last_error':
+                continue
+            declared = [re.sub(r'\[.*\]', '', p).replace('*', ' ').split()[-1] for p in prototypes[name][1]]
+            given = list(inspect.signature(member).parameters)[1:]
+            assert len(given) == len(declared), f'{cls.__name__}.{name}: {given} vs {declared}'
+            checked += 1
+    assert checked >= 10
