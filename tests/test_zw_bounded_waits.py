@@ -54,8 +54,11 @@ def test_check_status_reports_and_clear_status_recovers(cp1):
     from fused_gemm_a2a import FusedGemmA2AWorkspace
     ws = FusedGemmA2AWorkspace(512, 4, 256)
     ws.comm.check_status()
-    ws.comm.status.copy_(torch.tensor([2, 10, 7, 0], dtype=torch.int32))      # as a kernel would leave it
-    with pytest.raises(RuntimeError, match='device error 2.*where=10, detail=7'):
-        ws.comm.check_status()
-    ws.comm.clear_status()
+    try:
+        ws.comm.status.copy_(torch.tensor([2, 10, 7, 0], dtype=torch.int32))  # as a kernel would leave it
+        with pytest.raises(RuntimeError, match='device error 2.*where=10, detail=7'):
+            ws.comm.check_status()
+    finally:
+        ws.comm.clear_status()      # the group's status word is shared by every later test of the session
     ws.comm.check_status()
+    assert ws.comm.status.tolist() == [0, 0, 0, 0]
