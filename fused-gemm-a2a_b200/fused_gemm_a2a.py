@@ -47,6 +47,12 @@ WGRAD_BACKEND = os.environ.get('FUSED_WGRAD_BACKEND', 'torch')
 if WGRAD_BACKEND not in ('torch', 'fused_accum'):
     raise ValueError('FUSED_WGRAD_BACKEND must be torch or fused_accum')
 
+# Debug aid, off by default: with FGA_CHECK_TOKENS=1 every forward first checks on the host that all
+# ranks of the CP group pass the same local token count (one small all-reduce, so not for production
+# steps and skipped during graph capture). Ranks that disagree would otherwise wait, until the
+# device time limit, for row blocks that never arrive.
+CHECK_TOKENS = os.environ.get('FGA_CHECK_TOKENS', '0') == '1'
+
 _ALIGN = 1024        # every region of a slab starts on a 1 KiB boundary
 _HANDLE_BYTES = 64   # size of an exported memory handle (FGA_IPC_HANDLE_BYTES)
 _ROW_TILE = MMA_TILER_MN[0]   # rows of a CTA pair: capacities are multiples of it
@@ -686,6 +692,18 @@ def _check_workspace(workspace, module, tensor):
     workspace._validate(module, tensor)
 
 
+def _agree_on_tokens(comm, tokens):
+    """All ranks of the group must call with the same local token count (reference README: equal M
+    on every rank). Collective; raises the same ValueError on every rank when they differ."""
+    if comm.p == 1 or torch.cuda.is_current_stream_capturing():
+        return
+    span = torch.tensor([tokens, -tokens], dtype=torch.int64, device=comm.device)
+    dist.all_reduce(span, op=dist.ReduceOp.MIN, group=comm.group)
+    fewest, most = int(span[0]), -int(span[1])
+    if fewest != most:
+        raise ValueError(f'All CP ranks must pass the same number of local tokens; this group has {fewest} to {most}')
+
+
 class _CallerOwnedProjection(nn.Module):
     """What both projections share: weight and bias are caller-owned tensors kept by reference
     (never copied, never initialised), checked once at construction."""
@@ -734,6 +752,8 @@ class FusedQKVProjection(_CallerOwnedProjection):
     def forward(self, x, workspace):
         _check_workspace(workspace, self, x)
         _check(x, (x.shape[0], self.weight.shape[1]), 'x')
+        if CHECK_TOKENS:
+            _agree_on_tokens(workspace.comm, x.shape[0])
         return _FusedQKV.apply(x, self.weight, self.bias, self, workspace._view(x.shape[0], self.segments))
 
 
@@ -757,4 +777,6 @@ class FusedOutputProjection(_CallerOwnedProjection):
         if o.shape[0] % peers:
             raise ValueError('Token count must be divisible by CP')
         tokens = o.shape[0] // peers
+        if CHECK_TOKENS:
+            _agree_on_tokens(workspace.comm, tokens)
         return _FusedOutput.apply(o, self.weight, self.bias, self, workspace._view(tokens, 1), tokens)

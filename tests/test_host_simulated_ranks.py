@@ -206,3 +206,53 @@ def test_modules_on_simulated_ranks_match_the_oracle(world):
         # at least 3 BF16 cases x 3 token counts x (6 barriers + 4 GEMMs + 2 weight gradients + 2 row copies)
         # plus the MXFP8 cases
         assert detail > 3 * 3 * 14
+
+
+def mismatch_worker(rank, world, port, queue):
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    verdict = 'no error'
+    try:
+        fused.CHECK_TOKENS = True
+        ws = fused.FusedGemmA2AWorkspace(512, 4, 300)
+        qkv = fused.FusedQKVProjection(512, 4, weight=torch.zeros(1536, 512, dtype=BF))
+        proj = fused.FusedOutputProjection(512, 4, weight=torch.zeros(512, 512, dtype=BF))
+        before = sim.launches
+        for module, tensor in ((qkv, torch.zeros(129 + rank, 512, dtype=BF)),
+                               (proj, torch.zeros(world * (129 + rank), 4 // world, 128, dtype=BF))):
+            try:
+                module(tensor, ws)
+            except ValueError as error:
+                verdict = str(error)
+            else:
+                verdict = 'no error'
+                break
+        if sim.launches != before:
+            verdict = 'kernels were launched'
+        qkv(torch.zeros(200, 512, dtype=BF), ws)          # equal counts pass, and the ranks are still in step
+    finally:
+        fused.CHECK_TOKENS = False
+        undo()
+    queue.put((rank, verdict))
+    dist.destroy_process_group()
+
+
+def test_unequal_token_counts_are_caught_on_the_host_when_asked():
+    """FGA_CHECK_TOKENS: two ranks calling with 129 and 130 tokens both get the same ValueError from
+    either projection before anything is launched, and go on together afterwards."""
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=mismatch_worker, args=(r, 2, 29669, queue)) for r in range(2)]
+    for proc in procs:
+        proc.start()
+    results = sorted(queue.get(timeout=300) for _ in range(2))
+    for proc in procs:
+        proc.join(timeout=60)
+    for rank, verdict in results:
+        assert 'same number of local tokens' in verdict and '129 to 130' in verdict, (rank, verdict)
