@@ -72,6 +72,38 @@ def flops_per_step(m, hidden, segments):
     return dict(qkv_fwd=qkv, qkv_bwd=2 * qkv, out_fwd=out, out_bwd=2 * out, total=3 * (qkv + out))
 
 
+def provenance(torch=None):
+    """What produced the line: versions, the GPU, every tuning variable that was set, and a digest of
+    the built library and of the sources that define the path (as the reference's benchmark records
+    the digest of its two source files)."""
+    import hashlib
+
+    def digest(*paths):
+        h = hashlib.sha256()
+        for path in paths:
+            try:
+                with open(path, 'rb') as f:
+                    h.update(f.read())
+            except OSError:
+                return None
+        return h.hexdigest()[:16]
+
+    package = os.path.join(ROOT, 'fused-gemm-a2a_b200')
+    csrc = os.path.join(package, 'csrc')
+    sources = sorted(os.path.join(csrc, name) for name in os.listdir(csrc)) if os.path.isdir(csrc) else []
+    info = dict(tunables={k: v for k, v in sorted(os.environ.items()) if k.startswith(('FGA_', 'FUSED_'))},
+                libfga_sha256=digest(os.path.join(package, 'libfga.so')),
+                csrc_sha256=digest(*sources),
+                host_layer_sha256=digest(os.path.join(package, 'fused_gemm_a2a.py'),
+                                         os.path.join(package, 'fused_gemm_a2a_kernels.py')))
+    if torch is not None:
+        info['torch'] = torch.__version__
+        info['cuda'] = torch.version.cuda
+        if torch.cuda.is_available():
+            info['gpu'] = torch.cuda.get_device_name(torch.cuda.current_device())
+    return info
+
+
 def measured_peaks():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -599,7 +631,7 @@ def run_gpu_arm(args):
         step_roofline=dict(compute_ms_at_2250=flops['total'] / NOMINAL_BF16_TFLOPS / 1e9,
                            link_ms_at_770GBs=link_ms,
                            frac=max(flops['total'] / NOMINAL_BF16_TFLOPS / 1e9, link_ms) / ms_per_step),
-        clocks=clocks.summary(), gpu_launches=int(gpu_launches))
+        clocks=clocks.summary(), gpu_launches=int(gpu_launches), provenance=provenance(torch))
     if roofline is not None:
         line['roofline'] = roofline
     if e2e is not None:

@@ -75,3 +75,17 @@ def test_cpu_arm_prints_one_contract_line():
     assert line['cpu_baseline']['value'] == line['value'] == line['e2e']['value'] > 0
     assert line['e2e']['h2d_bytes_per_step'] == 0 and line['e2e']['d2h_bytes_per_step'] == 0
     assert 'workload' in line['config']
+
+
+def test_provenance_names_versions_tunables_and_digests(monkeypatch):
+    import torch
+
+    import bench
+    monkeypatch.setenv('FGA_PUSH_PAIRS', '4')
+    info = bench.provenance(torch)
+    assert info['tunables'] == {k: v for k, v in os.environ.items() if k.startswith(('FGA_', 'FUSED_'))}
+    assert info['tunables']['FGA_PUSH_PAIRS'] == '4'
+    assert info['torch'] == torch.__version__
+    for key in ('libfga_sha256', 'csrc_sha256', 'host_layer_sha256'):
+        assert info[key] is None or len(info[key]) == 16
+    assert info['csrc_sha256'] is not None and info['host_layer_sha256'] is not None
