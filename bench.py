@@ -88,6 +88,13 @@ def provenance(torch=None):
                 return None
         return h.hexdigest()[:16]
 
+    try:
+        return _provenance(torch, digest)
+    except Exception as error:      # never let bookkeeping break a measurement
+        return dict(error=f'{type(error).__name__}: {error}')
+
+
+def _provenance(torch, digest):
     package = os.path.join(ROOT, 'fused-gemm-a2a_b200')
     csrc = os.path.join(package, 'csrc')
     sources = sorted(os.path.join(csrc, name) for name in os.listdir(csrc)) if os.path.isdir(csrc) else []
