@@ -342,7 +342,6 @@ __device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job
   const int pieces_per_row = hpr / upp;
   const int chunk_row_bytes = upp * 256;
   const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
-  const int jobs_per_block = P.num_in * P.p * P.split;
   const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
   const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
   uint32_t seq = ring.seq, parity = ring.parity;
