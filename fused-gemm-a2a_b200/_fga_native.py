@@ -41,6 +41,11 @@ def _declare(l):
     l.fga_symm_open.argtypes = [c_char_p, pp]
     l.fga_symm_close.argtypes = [vp]
     l.fga_symm_free.argtypes = [vp]
+    l.fga_symm_vmm_size.argtypes = [c_size_t]
+    l.fga_symm_vmm_size.restype = i64
+    l.fga_symm_alloc_vmm.argtypes = [c_size_t, pp, POINTER(c_int)]
+    l.fga_symm_open_vmm.argtypes = [i, c_size_t, pp]
+    l.fga_symm_release_vmm.argtypes = [vp, c_size_t]
     l.fga_barrier.argtypes = [vp, vp, i, i, i, vp, i, vp, vp, c_uint64, vp]
     l.fga_gemm_push.argtypes = [vp, i, i, i, vp, i, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
     l.fga_gemm_recv.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, vp, vp, vp,
@@ -58,7 +63,7 @@ def _declare(l):
     l.fga_bias_grad_static.argtypes = [vp, i64, i, vp, i, i, vp]
     l.fga_mx_quantize.argtypes = [vp, i64, i, i64, i64, vp, vp, i64, i, vp]
     for name in ('fga_symm_alloc', 'fga_symm_export', 'fga_symm_open', 'fga_symm_close',
-                 'fga_symm_free', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
+                 'fga_symm_free', 'fga_symm_alloc_vmm', 'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
                  'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
                  'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
                  'fga_mx_quantize'):
@@ -66,7 +71,8 @@ def _declare(l):
 
 
 EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 'fga_symm_alloc', 'fga_symm_export',
-           'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_barrier', 'fga_gemm_push',
+           'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_symm_vmm_size', 'fga_symm_alloc_vmm',
+           'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push',
            'fga_gemm_recv', 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
            'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
            'fga_bias_grad', 'fga_bias_grad_static_capacity_floats', 'fga_bias_grad_static', 'fga_mx_quantize')

@@ -77,6 +77,87 @@ int encode_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype
   return kSuccess;
 }
 
+// ---- virtual-memory-management allocations -----------------------------------------------------
+// Driver entry points are looked up through the runtime, so the library does not link libcuda.
+struct VmmApi {
+  PFN_cuMemGetAllocationGranularity_v10020 granularity = nullptr;
+  PFN_cuMemCreate_v10020 create = nullptr;
+  PFN_cuMemRelease_v10020 release = nullptr;
+  PFN_cuMemAddressReserve_v10020 reserve = nullptr;
+  PFN_cuMemAddressFree_v10020 address_free = nullptr;
+  PFN_cuMemMap_v10020 map = nullptr;
+  PFN_cuMemUnmap_v10020 unmap = nullptr;
+  PFN_cuMemSetAccess_v10020 set_access = nullptr;
+  PFN_cuMemExportToShareableHandle_v10020 export_handle = nullptr;
+  PFN_cuMemImportFromShareableHandle_v10020 import_handle = nullptr;
+  bool complete = false;
+};
+
+template <typename Fn>
+static bool driver_entry(const char* name, Fn& fn) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return false;
+  fn = reinterpret_cast<Fn>(p);
+  return fn != nullptr;
+}
+
+static const VmmApi& vmm_api() {
+  static VmmApi api;
+  if (!api.complete) {
+    VmmApi a;
+    a.complete = driver_entry("cuMemGetAllocationGranularity", a.granularity) &&
+                 driver_entry("cuMemCreate", a.create) && driver_entry("cuMemRelease", a.release) &&
+                 driver_entry("cuMemAddressReserve", a.reserve) &&
+                 driver_entry("cuMemAddressFree", a.address_free) && driver_entry("cuMemMap", a.map) &&
+                 driver_entry("cuMemUnmap", a.unmap) && driver_entry("cuMemSetAccess", a.set_access) &&
+                 driver_entry("cuMemExportToShareableHandle", a.export_handle) &&
+                 driver_entry("cuMemImportFromShareableHandle", a.import_handle);
+    if (a.complete) api = a;
+  }
+  return api;
+}
+
+static int vmm_fail(CUresult r, const char* what) {
+  return set_error(kCudaError, "%s failed with CUresult %d", what, static_cast<int>(r));
+}
+
+static CUmemAllocationProp vmm_properties(int device) {
+  CUmemAllocationProp prop{};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  return prop;
+}
+
+// Reserve an address range for `handle`, map it and give the current device read/write access.
+// On failure nothing stays reserved or mapped.
+static int vmm_map(const VmmApi& api, CUmemGenericAllocationHandle handle, size_t size, size_t granularity,
+                   int device, void** out) {
+  CUdeviceptr va = 0;
+  CUresult r = api.reserve(&va, size, granularity, 0, 0);
+  if (r != CUDA_SUCCESS) return vmm_fail(r, "cuMemAddressReserve");
+  r = api.map(va, size, 0, handle, 0);
+  if (r != CUDA_SUCCESS) {
+    api.address_free(va, size);
+    return vmm_fail(r, "cuMemMap");
+  }
+  CUmemAccessDesc access{};
+  access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  access.location.id = device;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = api.set_access(va, size, &access, 1);
+  if (r != CUDA_SUCCESS) {
+    api.unmap(va, size);
+    api.address_free(va, size);
+    return vmm_fail(r, "cuMemSetAccess");
+  }
+  *out = reinterpret_cast<void*>(va);
+  return kSuccess;
+}
+
 }  // namespace fga
 
 using namespace fga;
@@ -127,6 +208,95 @@ int fga_symm_close(void* peer_ptr) {
 int fga_symm_free(void* ptr) {
   FGA_REQUIRE(ptr != nullptr, "fga_symm_free: null pointer");
   FGA_CUDA(cudaFree(ptr));
+  return kSuccess;
+}
+
+int64_t fga_symm_vmm_size(size_t bytes) {
+  const VmmApi& api = vmm_api();
+  int device = 0;
+  if (bytes == 0 || !api.complete || cudaGetDevice(&device) != cudaSuccess) {
+    set_error(kUnsupported, "fga_symm_vmm_size: no size, or the driver's virtual memory management API is not available");
+    return -1;
+  }
+  const CUmemAllocationProp prop = vmm_properties(device);
+  size_t granularity = 0;
+  if (api.granularity(&granularity, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || granularity == 0) {
+    set_error(kCudaError, "cuMemGetAllocationGranularity failed");
+    return -1;
+  }
+  return static_cast<int64_t>((bytes + granularity - 1) / granularity * granularity);
+}
+
+int fga_symm_alloc_vmm(size_t bytes, void** ptr, int* fd) {
+  FGA_REQUIRE(ptr != nullptr && fd != nullptr && bytes > 0, "fga_symm_alloc_vmm: need a size and two output pointers");
+  const VmmApi& api = vmm_api();
+  if (!api.complete) return set_error(kUnsupported, "the driver's virtual memory management API is not available");
+  int device = 0;
+  FGA_CUDA(cudaFree(nullptr));  // make sure the runtime has a context on the current device
+  FGA_CUDA(cudaGetDevice(&device));
+  const CUmemAllocationProp prop = vmm_properties(device);
+  size_t granularity = 0;
+  CUresult r = api.granularity(&granularity, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED);
+  if (r != CUDA_SUCCESS || granularity == 0) return vmm_fail(r, "cuMemGetAllocationGranularity");
+  const size_t size = (bytes + granularity - 1) / granularity * granularity;
+  CUmemGenericAllocationHandle handle = 0;
+  r = api.create(&handle, size, &prop, 0);
+  if (r != CUDA_SUCCESS) return vmm_fail(r, "cuMemCreate");
+  void* mapped = nullptr;
+  int rc = vmm_map(api, handle, size, granularity, device, &mapped);
+  int exported = -1;
+  if (rc == kSuccess) {
+    r = api.export_handle(&exported, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+    if (r != CUDA_SUCCESS) rc = vmm_fail(r, "cuMemExportToShareableHandle");
+  }
+  // The mapping (and every importer's) keeps the physical memory alive; the creation handle is not
+  // needed any longer.
+  api.release(handle);
+  if (rc == kSuccess) {
+    cudaError_t e = cudaMemset(mapped, 0, size);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) rc = cuda_fail(e, "cudaMemset");
+  }
+  if (rc != kSuccess) {
+    if (mapped != nullptr) {
+      api.unmap(reinterpret_cast<CUdeviceptr>(mapped), size);
+      api.address_free(reinterpret_cast<CUdeviceptr>(mapped), size);
+    }
+    return rc;
+  }
+  *ptr = mapped;
+  *fd = exported;
+  return kSuccess;
+}
+
+int fga_symm_open_vmm(int fd, size_t bytes, void** peer_ptr) {
+  FGA_REQUIRE(fd >= 0 && bytes > 0 && peer_ptr != nullptr, "fga_symm_open_vmm: need a descriptor, a size and an output pointer");
+  const VmmApi& api = vmm_api();
+  if (!api.complete) return set_error(kUnsupported, "the driver's virtual memory management API is not available");
+  int device = 0;
+  FGA_CUDA(cudaGetDevice(&device));
+  const CUmemAllocationProp prop = vmm_properties(device);
+  size_t granularity = 0;
+  CUresult r = api.granularity(&granularity, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED);
+  if (r != CUDA_SUCCESS || granularity == 0) return vmm_fail(r, "cuMemGetAllocationGranularity");
+  FGA_REQUIRE(bytes % granularity == 0, "fga_symm_open_vmm: the size must be the owner's fga_symm_vmm_size()");
+  CUmemGenericAllocationHandle handle = 0;
+  r = api.import_handle(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                        CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  if (r != CUDA_SUCCESS) return vmm_fail(r, "cuMemImportFromShareableHandle");
+  const int rc = vmm_map(api, handle, bytes, granularity, device, peer_ptr);
+  api.release(handle);  // the mapping holds its own reference
+  return rc;
+}
+
+int fga_symm_release_vmm(void* ptr, size_t bytes) {
+  FGA_REQUIRE(ptr != nullptr && bytes > 0, "fga_symm_release_vmm: null pointer or no size");
+  const VmmApi& api = vmm_api();
+  if (!api.complete) return set_error(kUnsupported, "the driver's virtual memory management API is not available");
+  CUresult r = api.unmap(reinterpret_cast<CUdeviceptr>(ptr), bytes);
+  if (r != CUDA_SUCCESS) return vmm_fail(r, "cuMemUnmap");
+  r = api.address_free(reinterpret_cast<CUdeviceptr>(ptr), bytes);
+  if (r != CUDA_SUCCESS) return vmm_fail(r, "cuMemAddressFree");
   return kSuccess;
 }
 

@@ -53,6 +53,14 @@ if WGRAD_BACKEND not in ('torch', 'fused_accum'):
 # device time limit, for row blocks that never arrive.
 CHECK_TOKENS = os.environ.get('FGA_CHECK_TOKENS', '0') == '1'
 
+# How symmetric buffers are allocated and mapped into the peers: 'ipc' = cudaMalloc + CUDA IPC memory
+# handles (the default), 'vmm' = the driver's virtual memory management API with POSIX file
+# descriptors passed over Unix-domain sockets. With 'vmm' every mapping holds a reference to the
+# physical memory, so a rank that exits does not invalidate what its peers still store into.
+SYMM_BACKEND = os.environ.get('FGA_SYMM', 'ipc')
+if SYMM_BACKEND not in ('ipc', 'vmm'):
+    raise ValueError('FGA_SYMM must be ipc or vmm')
+
 _ALIGN = 1024        # every region of a slab starts on a 1 KiB boundary
 _HANDLE_BYTES = 64   # size of an exported memory handle (FGA_IPC_HANDLE_BYTES)
 _ROW_TILE = MMA_TILER_MN[0]   # rows of a CTA pair: capacities are multiples of it
@@ -108,6 +116,48 @@ def exchange_handles(group, rank, peers, handle, local_address, open_peer):
             raise RuntimeError('Memory handle exchange returned a malformed entry')
         reachable.append(local_address if owner == rank else open_peer(raw))
     return reachable
+
+
+_socket_serial = iter(range(1 << 62))
+
+
+def exchange_descriptors(group, rank, peers, descriptor):
+    """Hand one open file descriptor of every rank to every other rank of the group (all on this
+    host): each rank listens on a Unix-domain socket in the abstract namespace, the socket names go
+    around with one all-gather, and every rank fetches its peers' descriptors as SCM_RIGHTS
+    messages. Returns P descriptors valid in this process: `descriptor` itself at [rank], received
+    duplicates (which the caller closes) elsewhere."""
+    import socket
+    import threading
+    name = f'\0fga-{os.getpid()}-{next(_socket_serial)}'
+    server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    server.bind(name)
+    server.listen(max(peers, 1))
+    names = [None] * peers
+    dist.all_gather_object(names, name, group=group)
+
+    def serve():
+        for _ in range(peers - 1):
+            connection, _ = server.accept()
+            with connection:
+                socket.send_fds(connection, [b'fd'], [descriptor])
+
+    server_thread = threading.Thread(target=serve, daemon=True)
+    server_thread.start()
+    received = []
+    for owner in range(peers):
+        if owner == rank:
+            received.append(descriptor)
+            continue
+        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
+            client.connect(names[owner])
+            _, descriptors, _, _ = socket.recv_fds(client, 16, 1)
+        if len(descriptors) != 1:
+            raise RuntimeError('Descriptor exchange returned a malformed message')
+        received.append(descriptors[0])
+    server_thread.join()
+    server.close()
+    return received
 
 
 class _Slab:
@@ -182,27 +232,57 @@ class _Comm:
     def symmetric_bytes(self, nbytes):
         """Allocate `nbytes` of zeroed device memory, map it into every peer and return
         (local address, list of P addresses of the same buffer as seen from this rank)."""
-        lib, ct = _native.lib(), _native.ctypes
-        local = _native.c_void_p()
-        _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
-        self._allocations.append(local.value)
-        if self.p == 1:
-            seen = [local.value]
-        else:
-            handle = ct.create_string_buffer(_HANDLE_BYTES)
-            _native.check(lib.fga_symm_export(local, handle))
-
-            def open_peer(raw):
-                remote = _native.c_void_p()
-                _native.check(lib.fga_symm_open(raw, ct.byref(remote)))
-                return remote.value
-
-            seen = exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer)
+        local, seen = self._map_everywhere_vmm(nbytes) if SYMM_BACKEND == 'vmm' else self._map_everywhere_ipc(nbytes)
+        self._allocations.append(local)
         usable = torch.tensor(int(all(address and address % 16 == 0 for address in seen)), device=self.device)
         if self.p > 1:
             dist.all_reduce(usable, op=dist.ReduceOp.MIN, group=self.group)
         if not usable.item():
             raise RuntimeError('Peer buffers must be aligned and GPU-addressable')
+        return local, seen
+
+    def _map_everywhere_ipc(self, nbytes):
+        """cudaMalloc + one 64-byte CUDA IPC handle per rank."""
+        lib, ct = _native.lib(), _native.ctypes
+        local = _native.c_void_p()
+        _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
+        if self.p == 1:
+            return local.value, [local.value]
+        handle = ct.create_string_buffer(_HANDLE_BYTES)
+        _native.check(lib.fga_symm_export(local, handle))
+
+        def open_peer(raw):
+            remote = _native.c_void_p()
+            _native.check(lib.fga_symm_open(raw, ct.byref(remote)))
+            return remote.value
+
+        return local.value, exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer)
+
+    def _map_everywhere_vmm(self, nbytes):
+        """Driver VMM allocation + one POSIX file descriptor per rank; every mapping keeps the
+        physical memory alive."""
+        lib, ct = _native.lib(), _native.ctypes
+        size = lib.fga_symm_vmm_size(nbytes)
+        if size < 0:
+            _native.check(-3)
+        local, descriptor = _native.c_void_p(), ct.c_int(-1)
+        _native.check(lib.fga_symm_alloc_vmm(nbytes, ct.byref(local), ct.byref(descriptor)))
+        seen = [local.value]
+        try:
+            if self.p > 1:
+                seen = []
+                for owner, received in enumerate(exchange_descriptors(self.group, self.rank, self.p, descriptor.value)):
+                    if owner == self.rank:
+                        seen.append(local.value)
+                        continue
+                    remote = _native.c_void_p()
+                    try:
+                        _native.check(lib.fga_symm_open_vmm(received, size, ct.byref(remote)))
+                    finally:
+                        os.close(received)
+                    seen.append(remote.value)
+        finally:
+            os.close(descriptor.value)
         return local.value, seen
 
     def _allocate(self, nbytes):

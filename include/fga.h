@@ -64,6 +64,25 @@ int fga_symm_open(const unsigned char handle[FGA_IPC_HANDLE_BYTES], void** peer_
 int fga_symm_close(void* peer_ptr);
 int fga_symm_free(void* ptr);
 
+/* The same buffers from the driver's virtual memory management API instead of cudaMalloc + CUDA IPC
+ * (opt-in; the Python layer selects it with FGA_SYMM=vmm). The physical memory is reference counted
+ * by every mapping, the owner's and each importer's, so a rank that exits does not pull the memory
+ * out from under peers that are still storing into it. The shareable handle is a POSIX file
+ * descriptor, which the host layer passes to the peers over a Unix-domain socket.
+ *   fga_symm_vmm_size(bytes)          bytes rounded up to the allocation granularity (-1 on error);
+ *                                      every rank maps this size.
+ *   fga_symm_alloc_vmm(bytes, &p, &fd) zero-filled memory of fga_symm_vmm_size(bytes) mapped at p for the
+ *                                      current device, and a descriptor for the peers (close it after
+ *                                      the exchange).
+ *   fga_symm_open_vmm(fd, size, &p)    map a peer's allocation of `size` = its fga_symm_vmm_size();
+ *                                      the descriptor may be closed afterwards.
+ *   fga_symm_release_vmm(p, size)      unmap either kind of mapping; the memory is freed with its
+ *                                      last mapping. */
+int64_t fga_symm_vmm_size(size_t bytes);
+int fga_symm_alloc_vmm(size_t bytes, void** ptr, int* fd);
+int fga_symm_open_vmm(int fd, size_t bytes, void** peer_ptr);
+int fga_symm_release_vmm(void* ptr, size_t bytes);
+
 /* ---- group barrier ------------------------------------------------------------------------
  * Replaces barrier / _barrier_kernel (fused_gemm_a2a_kernels.py:204-234; host wrapper
  * fused_gemm_a2a.py:129-135). flags: this rank's int64[P]; peer_flags: device int64[P] holding

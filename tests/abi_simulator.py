@@ -20,6 +20,7 @@ on host memory, following the header's contract (not the CUDA sources):
     the receive buffer once all arrivals are in, as the quantizer warps do.
 """
 import ctypes
+import mmap
 import os
 from multiprocessing import shared_memory
 
@@ -63,6 +64,7 @@ class SimulatedLibrary:
         self.created = []
         self.launches = 0
         self.quantized = []               # (payload tensor, BF16 matrix it was quantized from), kept alive
+        self.mappings = []                # memory-mapped descriptors of the VMM flavour
 
     def source_of(self, address):
         for payload, source in reversed(self.quantized):
@@ -94,6 +96,28 @@ class SimulatedLibrary:
 
     def fga_symm_open(self, raw, out):
         out._obj.value = self._map(shared_memory.SharedMemory(name=raw.rstrip(b'\0').decode()))
+        return 0
+
+    # The virtual-memory-management flavour: an anonymous memory file per allocation, whose descriptor
+    # the host layer passes to the peers exactly as it passes a CUDA shareable handle; each side maps it.
+    def fga_symm_vmm_size(self, nbytes):
+        return -(-int(nbytes) // mmap.PAGESIZE) * mmap.PAGESIZE
+
+    def _map_descriptor(self, descriptor, size):
+        mapping = mmap.mmap(descriptor, size)
+        self.mappings.append(mapping)
+        return ctypes.addressof(ctypes.c_char.from_buffer(mapping))
+
+    def fga_symm_alloc_vmm(self, nbytes, out, descriptor_out):
+        size = self.fga_symm_vmm_size(nbytes)
+        descriptor = os.memfd_create(f'{self.tag}_{self.rank}_{len(self.mappings)}')
+        os.ftruncate(descriptor, size)
+        out._obj.value = self._map_descriptor(descriptor, size)
+        descriptor_out._obj.value = descriptor
+        return 0
+
+    def fga_symm_open_vmm(self, descriptor, size, out):
+        out._obj.value = self._map_descriptor(descriptor, size)
         return 0
 
     def close(self, meet=True):

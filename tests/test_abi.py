@@ -71,7 +71,7 @@ def test_ctypes_signatures_match_the_header():
     import ctypes
     lib = _fga_native.lib()
     scalars = {'int': ctypes.c_int, 'int64_t': ctypes.c_int64, 'uint64_t': ctypes.c_uint64, 'size_t': ctypes.c_size_t}
-    pointers = (ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p))
+    pointers = (ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int))
     returns = {'int': ctypes.c_int, 'int64_t': ctypes.c_int64, 'uint64_t': ctypes.c_uint64,
                'const char*': ctypes.c_char_p, 'const char *': ctypes.c_char_p}
     prototypes = _prototypes()

@@ -62,7 +62,7 @@ def everyone(value):
     return box
 
 
-def run_rank(hidden, heads, capacity_tokens, token_counts):
+def run_rank(hidden, heads, capacity_tokens, token_counts, cases=None):
     import abi_simulator
     import fused_gemm_a2a as fused
     import numpy as np
@@ -79,7 +79,7 @@ def run_rank(hidden, heads, capacity_tokens, token_counts):
     sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
     completed = False
     try:
-        for case in CASES:
+        for case in (CASES if cases is None else cases):
             quantized = case['precision'] == 'mxfp8'
             if quantized and p > 2 and case['gate']:
                 continue      # the numpy MXFP8 oracle is slow and every rank evaluates it for all ranks
@@ -256,3 +256,51 @@ def test_unequal_token_counts_are_caught_on_the_host_when_asked():
         proc.join(timeout=60)
     for rank, verdict in results:
         assert 'same number of local tokens' in verdict and '129 to 130' in verdict, (rank, verdict)
+
+
+def vmm_worker(rank, world, port, queue):
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    import fused_gemm_a2a as fused
+    open_before = len(os.listdir('/proc/self/fd'))
+    fused.SYMM_BACKEND = 'vmm'
+    try:
+        launches = run_rank(hidden=512, heads=4, capacity_tokens=300, token_counts=(129,), cases=CASES[1:3])
+        leaked = len(os.listdir('/proc/self/fd')) - open_before
+        queue.put((rank, 'ok' if launches > 0 else 'nothing ran', leaked))
+    except BaseException as error:
+        import traceback
+        queue.put((rank, f'{type(error).__name__}: {error}\n{traceback.format_exc()[-2000:]}', 0))
+        queue.close()
+        queue.join_thread()
+        os._exit(1)
+    finally:
+        fused.SYMM_BACKEND = 'ipc'
+    dist.destroy_process_group()
+
+
+def test_descriptor_backed_buffers_carry_the_same_protocol(world=2):
+    """FGA_SYMM=vmm on CPU ranks: every allocation's file descriptor really travels to the peers over
+    Unix-domain sockets, each side maps it, and the projections match the oracle through those
+    mappings. No descriptor is left open afterwards (each rank closes its own and the received ones)."""
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=vmm_worker, args=(r, world, 29675 + world, queue)) for r in range(world)]
+    for proc in procs:
+        proc.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(queue.get(timeout=600))
+            assert results[-1][1] == 'ok', f'rank {results[-1][0]}: {results[-1][1]}'
+    finally:
+        for proc in procs:
+            proc.join(timeout=5 if results and results[-1][1] != 'ok' else 120)
+            if proc.is_alive():
+                proc.terminate()
+    for rank, _, leaked in results:
+        assert leaked <= 0, f'rank {rank} left {leaked} descriptors open'
