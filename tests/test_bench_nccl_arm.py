@@ -1,0 +1,82 @@
+"""The comparison arm of bench.py (`--impl nccl`: cuBLAS GEMMs + an all-to-all per projection) must
+compute the same projections as the fused path it is timed against. Here it runs on two and four
+CPU ranks under gloo in FP32 and is compared with the oracle: same outputs, same gradients, same
+head-side layouts."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def worker(rank, world, port, queue):
+    for path in (ROOT, os.path.join(ROOT, 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    import bench
+    from oracle.ulysses_oracle import UlyssesOracle, interleave_qkv_rows
+    hidden, heads, tokens, segments = 256, 4, 5, 3
+    d = hidden // heads
+    g = torch.Generator().manual_seed(7)
+    w_seg = torch.randn(segments * hidden, hidden, generator=g) / hidden ** 0.5      # segment-major [Q; K; V]
+    wo = torch.randn(hidden, hidden, generator=g) / hidden ** 0.5
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(tokens, hidden, generator=g)
+    grads = [torch.randn(world * tokens, heads // world, d, generator=g) for _ in range(segments)]
+    o = torch.randn(world * tokens, heads // world, d, generator=g)
+    dy = torch.randn(tokens, hidden, generator=g)
+    arm = bench.NcclUnfused(torch, dist, world, hidden, heads, list(w_seg.split(hidden)), wo)
+    outs = arm.qkv_forward(x)
+    dx, dws = arm.qkv_backward(x, grads)
+    y = arm.out_forward(o)
+    do, dwo = arm.out_backward(dy)
+
+    def everyone(value):
+        box = [None] * world
+        dist.all_gather_object(box, value)
+        return box
+
+    oracle = UlyssesOracle(world, hidden, heads, segments, interleave_qkv_rows(w_seg, heads, d), None, wo, None,
+                           dtype=torch.float32)
+    xs, all_grads, all_o, dys = everyone(x), everyone(tuple(grads)), everyone(o), everyone(dy)
+    problems = []
+
+    def same(actual, expected, what):
+        if actual.shape != expected.shape or not torch.allclose(actual, expected, rtol=1e-4, atol=1e-4):
+            problems.append(what)
+
+    for name, got, want in zip('qkv', outs, oracle.qkv_forward(xs)[rank]):
+        same(got, want, name)
+    rdx, rdw, _ = oracle.qkv_backward(xs, all_grads)[rank]
+    same(dx, rdx, 'dx')
+    # the arm keeps one weight per segment (dws comes back last segment first); the oracle's is interleaved per head
+    per_segment = torch.cat(list(reversed(dws)))
+    same(interleave_qkv_rows(per_segment, heads, d), rdw, 'dW_qkv')
+    same(y, oracle.out_forward(all_o)[rank], 'y')
+    rdos, rparams = oracle.out_backward(all_o, dys)
+    same(do, rdos[rank], 'dO')
+    same(dwo, rparams[rank][0], 'dW_o')
+    queue.put((rank, problems))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_comparison_arm_computes_the_same_projections(world):
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, world, 29720 + world, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, problems in results:
+        assert problems == [], f'rank {rank}: {problems}'
