@@ -219,7 +219,7 @@ class _Comm:
         self.compiled = {}                # launch plans by geometry (nothing is compiled; kept for introspection)
         self.pool = {}
         self.projection_buffers = {}
-        self._allocations = []
+        self._allocations = []            # (backend, local address, addresses as seen from here, mapped bytes)
         self.flags, self.peer_flags = self.symmetric((self.p,), torch.int64)
         self.epoch = self._words(1)
         torch.cuda.synchronize()
@@ -232,8 +232,11 @@ class _Comm:
     def symmetric_bytes(self, nbytes):
         """Allocate `nbytes` of zeroed device memory, map it into every peer and return
         (local address, list of P addresses of the same buffer as seen from this rank)."""
-        local, seen = self._map_everywhere_vmm(nbytes) if SYMM_BACKEND == 'vmm' else self._map_everywhere_ipc(nbytes)
-        self._allocations.append(local)
+        if SYMM_BACKEND == 'vmm':
+            local, seen, mapped = self._map_everywhere_vmm(nbytes)
+        else:
+            local, seen, mapped = self._map_everywhere_ipc(nbytes)
+        self._allocations.append((SYMM_BACKEND, local, list(seen), mapped))
         usable = torch.tensor(int(all(address and address % 16 == 0 for address in seen)), device=self.device)
         if self.p > 1:
             dist.all_reduce(usable, op=dist.ReduceOp.MIN, group=self.group)
@@ -247,7 +250,7 @@ class _Comm:
         local = _native.c_void_p()
         _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
         if self.p == 1:
-            return local.value, [local.value]
+            return local.value, [local.value], nbytes
         handle = ct.create_string_buffer(_HANDLE_BYTES)
         _native.check(lib.fga_symm_export(local, handle))
 
@@ -256,7 +259,7 @@ class _Comm:
             _native.check(lib.fga_symm_open(raw, ct.byref(remote)))
             return remote.value
 
-        return local.value, exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer)
+        return local.value, exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer), nbytes
 
     def _map_everywhere_vmm(self, nbytes):
         """Driver VMM allocation + one POSIX file descriptor per rank; every mapping keeps the
@@ -283,7 +286,30 @@ class _Comm:
                     seen.append(remote.value)
         finally:
             os.close(descriptor.value)
-        return local.value, seen
+        return local.value, seen, size
+
+    def release(self):
+        """Give every symmetric buffer of this group back. Collective: all ranks synchronize their
+        device and meet first, so that nobody still stores into memory that is about to be unmapped;
+        then each rank unmaps its peers' buffers and frees its own. Workspaces, views and tensors
+        that came from this object must not be used afterwards; the next workspace of the group
+        builds a new runtime."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        lib = _native.lib()
+        for backend, local, seen, mapped in self._allocations:
+            for owner, address in enumerate(seen):
+                if owner == self.rank:
+                    continue
+                _native.check(lib.fga_symm_release_vmm(address, mapped) if backend == 'vmm'
+                              else lib.fga_symm_close(address))
+            _native.check(lib.fga_symm_release_vmm(local, mapped) if backend == 'vmm' else lib.fga_symm_free(local))
+        self._allocations.clear()
+        self.pool.clear()
+        self.projection_buffers.clear()
+        for slot in [slot for slot, comm in type(self)._instances.items() if comm is self]:
+            del type(self)._instances[slot]
+        dist.barrier(self.group)
 
     def _allocate(self, nbytes):
         base, peer_bases = self.symmetric_bytes(nbytes)

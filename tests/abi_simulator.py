@@ -65,6 +65,7 @@ class SimulatedLibrary:
         self.launches = 0
         self.quantized = []               # (payload tensor, BF16 matrix it was quantized from), kept alive
         self.mappings = []                # memory-mapped descriptors of the VMM flavour
+        self.released = []                # what the host layer gave back, in order
 
     def source_of(self, address):
         for payload, source in reversed(self.quantized):
@@ -118,6 +119,18 @@ class SimulatedLibrary:
 
     def fga_symm_open_vmm(self, descriptor, size, out):
         out._obj.value = self._map_descriptor(descriptor, size)
+        return 0
+
+    def fga_symm_close(self, address):
+        self.released.append(('close', int(address)))
+        return 0
+
+    def fga_symm_free(self, address):
+        self.released.append(('free', int(address)))
+        return 0
+
+    def fga_symm_release_vmm(self, address, size):
+        self.released.append(('release', int(address), int(size)))
         return 0
 
     def close(self, meet=True):

@@ -304,3 +304,54 @@ def test_descriptor_backed_buffers_carry_the_same_protocol(world=2):
                 proc.terminate()
     for rank, _, leaked in results:
         assert leaked <= 0, f'rank {rank} left {leaked} descriptors open'
+
+
+def release_worker(rank, world, port, queue, backend):
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    fused.SYMM_BACKEND = backend
+    try:
+        ws = fused.FusedGemmA2AWorkspace(512, 4, 300)
+        comm = ws.comm
+        allocations = list(comm._allocations)
+        comm.release()
+        again = fused.FusedGemmA2AWorkspace(512, 4, 300)          # a fresh runtime, fresh buffers
+        report = dict(allocations=len(allocations), released=list(sim.released),
+                      expected=[(kind, local, seen, mapped) for kind, local, seen, mapped in allocations],
+                      fresh=again.comm is not comm and len(again.comm._allocations) == len(allocations),
+                      emptied=not comm._allocations and not comm.projection_buffers)
+        queue.put((rank, report))
+    finally:
+        fused.SYMM_BACKEND = 'ipc'
+        undo()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('backend', ['ipc', 'vmm'])
+def test_release_unmaps_every_peer_and_frees_every_buffer_once(backend):
+    world = 2
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=release_worker, args=(r, world, 29730 + len(backend), queue, backend)) for r in range(world)]
+    for proc in procs:
+        proc.start()
+    results = sorted(queue.get(timeout=300) for _ in range(world))
+    for proc in procs:
+        proc.join(timeout=60)
+        assert proc.exitcode == 0
+    for rank, report in results:
+        assert report['allocations'] == 3 and report['fresh'] and report['emptied']      # flags + two buffer sets
+        wanted = []
+        for kind, local, seen, mapped in report['expected']:
+            assert kind == backend
+            for owner, address in enumerate(seen):
+                if owner != rank:
+                    wanted.append(('release', address, mapped) if backend == 'vmm' else ('close', address))
+            wanted.append(('release', local, mapped) if backend == 'vmm' else ('free', local))
+        assert report['released'] == wanted
