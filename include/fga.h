@@ -19,6 +19,11 @@
  *     memory (the peer that did not answer may have exited and unmapped it). The host reads the
  *     word, tears the group down or repairs it, and zeroes the word before it launches again.
  *   - all matrices are row-major; BF16 is passed as 16-bit words.
+ *   - tuning variables are read from the environment at every launch: FGA_STAGES, FGA_GROUP_M_PUSH,
+ *     FGA_GROUP_M_RECV, FGA_GROUP_M_LOCAL (raster group sizes), FGA_PUSHER_WARPS, FGA_PUSH_LEAD,
+ *     FGA_PUSH_PAIRS (recv launches: CTA pairs that only push), FGA_WGRAD_SPLITS (fga_gemm_local with
+ *     FP32 output: shares of the reduction axis per tile, a number or "auto"). Unset means the
+ *     defaults that were measured; none of them changes results beyond FP32 summation order.
  */
 #ifndef FGA_H_
 #define FGA_H_
