@@ -64,3 +64,36 @@ def test_receive_steady_phase_and_pushing_only_ctas(native, monkeypatch, p, hidd
     monkeypatch.setenv('FGA_GROUP_M_RECV', '1')
     monkeypatch.setenv('FGA_PUSH_PAIRS', str(push_pairs))
     receive_case(native, p, hidden, heads, tokens, num_in)
+
+
+def test_vmm_allocation_is_shared_through_its_descriptor_and_outlives_the_first_mapping(native):
+    """FGA_SYMM=vmm on one GPU: the allocation's file descriptor is imported again in the same
+    process, which gives a second mapping of the same physical memory (what a peer process gets).
+    Stores through one mapping are read through the other, and after the owner's mapping is released
+    the memory is still there for the remaining one."""
+    import ctypes
+
+    from fused_gemm_a2a import _wrap
+    dev = torch.device('cuda', 0)
+    wanted = 3 << 20
+    size = native.fga_symm_vmm_size(wanted)
+    assert size >= wanted, native.fga_last_error()
+    owner, alias, descriptor = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int(-1)
+    assert native.fga_symm_alloc_vmm(wanted, ctypes.byref(owner), ctypes.byref(descriptor)) == 0, native.fga_last_error()
+    try:
+        assert native.fga_symm_open_vmm(descriptor.value, size, ctypes.byref(alias)) == 0, native.fga_last_error()
+    finally:
+        os.close(descriptor.value)
+    assert owner.value and alias.value and owner.value != alias.value and owner.value % 256 == 0
+    first, second = _wrap(owner.value, size, dev), _wrap(alias.value, size, dev)
+    assert int(first.sum()) == 0                      # zero-filled
+    first[:4096] = 7
+    second[size - 4096:] = 9
+    torch.cuda.synchronize()
+    assert bool((second[:4096] == 7).all()) and bool((first[size - 4096:] == 9).all())
+    del first
+    assert native.fga_symm_release_vmm(owner.value, size) == 0, native.fga_last_error()
+    torch.cuda.synchronize()
+    assert bool((second[:4096] == 7).all()) and int(second[4096:size - 4096].sum()) == 0
+    del second
+    assert native.fga_symm_release_vmm(alias.value, size) == 0, native.fga_last_error()
