@@ -282,3 +282,66 @@ def test_scale_bytes_fill_the_tcgen05_blocks_exactly(sched):
         # one 512-byte block per (128 rows, 4 groups); the four groups of a row are adjacent bytes
         assert np.array_equal(offsets // 512, (np.arange(rows)[:, None] // 128) * (groups // 4) + np.arange(groups)[None, :] // 4)
         assert np.array_equal(offsets[:, 1] - offsets[:, 0], np.ones(rows, dtype=offsets.dtype))
+
+
+# ------------------------------------------------------------------------------------ randomized sweeps
+def test_random_geometries_keep_the_exactly_once_properties(sched):
+    """300 random geometries (fixed seed): raster and K shares cover every (tile, K step) once under a
+    random grid size; the pusher schedule with a random number of pushing-only pairs runs every job
+    once; a job's chunks cover its rows and units once."""
+    import random
+    rng = random.Random(20251125)
+    for _ in range(300):
+        m_tiles, n_tiles = rng.randint(1, 40), rng.randint(1, 24)
+        group_m, pairs = rng.randint(1, 20), rng.randint(1, 80)
+        k_splits = rng.choice([1, 1, 2, 3, 5, 8])
+        k_tiles = rng.randint(k_splits, 40)
+        total = m_tiles * n_tiles
+        seen = set()
+        for pair in range(min(pairs, total * k_splits)):
+            for u in range(pair, total * k_splits, pairs):
+                t, kt0, kt1 = unit_of(sched, k_tiles, k_splits, total, u)
+                m, n = tile_of(sched, m_tiles, n_tiles, group_m, t)
+                assert 0 <= m < m_tiles and 0 <= n < n_tiles and kt0 < kt1
+                for kt in range(kt0, kt1):
+                    assert (m, n, kt) not in seen
+                    seen.add((m, n, kt))
+        assert len(seen) == total * k_tiles
+
+        p, num_in = rng.choice([1, 2, 4, 8]), rng.choice([1, 3, 4])
+        split = rng.choice([1, 2, 4, 8, 16])
+        jobs = sched.sched_push_jobs_total(m_tiles, num_in, p, split)
+        first = sched.sched_first_phase_jobs(m_tiles, group_m, num_in, p, split)
+        grid = 2 * rng.randint(1, 74)
+        push_pairs = rng.randint(0, grid // 2 - 1)
+        runs = [0] * jobs
+        for cta in range(grid):
+            for warp in range(4):
+                for job in range(cta * 4 + warp, first, grid * 4):
+                    runs[job] += 1
+        if push_pairs:
+            gemm_ctas = grid - 2 * push_pairs
+            for cta in range(gemm_ctas, grid):
+                for warp in range(10):
+                    for job in range(first + (cta - gemm_ctas) * 10 + warp, jobs, 2 * push_pairs * 10):
+                        runs[job] += 1
+        else:
+            warps = rng.randint(1, 4)
+            for cta in range(grid):
+                for warp in range(warps):
+                    for job in range(first + cta * warps + warp, jobs, grid * warps):
+                        runs[job] += 1
+        assert runs == [1] * jobs
+
+        hpr, sub_rows = rng.randint(1, 40), 128 // split
+        units, rows = chunking(sched, hpr, sub_rows)
+        assert 1 <= units <= 16 and hpr % units == 0 and units * rows * 256 <= 4096 and sub_rows % rows == 0
+        covered = torch.zeros(sub_rows, hpr, dtype=torch.int32)
+        out = (I * 3)()
+        src_rows, row0 = rng.randint(1, 400), rng.choice([0, 128, 256]) + rng.randrange(0, 128, sub_rows)
+        for c in range(sched.sched_push_chunks_per_job(hpr, units, rows, sub_rows)):
+            sched.sched_push_chunk(c, hpr, units, rows, src_rows, row0, out)
+            r0, u0, valid = tuple(out)
+            covered[r0:r0 + rows, u0:u0 + units] += 1
+            assert valid == max(0, min(rows, src_rows - (row0 + r0)))
+        assert bool((covered == 1).all())
