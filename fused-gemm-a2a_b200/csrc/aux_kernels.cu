@@ -161,13 +161,13 @@ int launch_copy_rank_rows(const void* const* in, void* const* out, int segments,
 constexpr int kBiasPartRows = 256;
 
 __global__ void bias_grad_partial_kernel(const uint16_t* dy, float* partial, long long rows,
-                                         int width) {
+                                         int width, bool vec) {
   const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (col >= width) return;
   const long long r0 = static_cast<long long>(blockIdx.y) * kBiasPartRows;
   const long long r1 = min(rows, r0 + kBiasPartRows);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (col + 8 <= width && width % 8 == 0) {
+  if (vec) {  // host-checked: width % 8 == 0 and a 16-byte aligned base, so every row piece is aligned
     const uint16_t* p = dy + r0 * width + col;
 #pragma unroll 4
     for (long long r = r0; r < r1; ++r, p += width) {
@@ -214,8 +214,9 @@ int launch_bias_grad(const void* dy, long long rows, int width, void* out, int o
   const int parts = static_cast<int>((rows + kBiasPartRows - 1) / kBiasPartRows);
   const int threads = 128;
   dim3 grid1((width + threads * 8 - 1) / (threads * 8), parts);
+  const bool vec = width % 8 == 0 && reinterpret_cast<uintptr_t>(dy) % 16 == 0;
   bias_grad_partial_kernel<<<grid1, threads, 0, stream>>>(static_cast<const uint16_t*>(dy), scratch,
-                                                          rows, width);
+                                                          rows, width, vec);
   FGA_LAUNCHED();
   dim3 grid2((width + threads - 1) / threads);
   if (out_is_f32)
@@ -246,19 +247,22 @@ long long bias_grad_static_capacity_floats() { return kStaticScratchFloats; }
 
 // Device address of the array for the current device. In host code the symbol is only a stand-in,
 // never a device pointer, so the address is looked up once per device with that device current.
+// The cache is read and written with atomics: two host threads may make a device's first call at
+// the same time, and both then store the same address. (It does not survive cudaDeviceReset; a
+// process that resets a device must not call this entry point on it afterwards.)
 static int static_scratch_address(float** out) {
   constexpr int kMaxDevices = 64;
   static float* cached[kMaxDevices];  // null = not looked up yet on that device
   int dev = 0;
   FGA_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return set_error(kUnsupported, "device index %d out of range", dev);
-  if (cached[dev] == nullptr) {
-    float* address = nullptr;
+  float* address = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (address == nullptr) {
     FGA_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_bias_scratch));
     if (address == nullptr) return set_error(kCudaError, "the static scratch array has no device address");
-    cached[dev] = address;
+    __atomic_store_n(&cached[dev], address, __ATOMIC_RELEASE);
   }
-  *out = cached[dev];
+  *out = address;
   return kSuccess;
 }
 

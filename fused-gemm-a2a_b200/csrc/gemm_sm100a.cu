@@ -8,22 +8,11 @@
 
 namespace fga {
 
-// CTA pairs that only push in recv launches (see GemmParams::push_pairs); FGA_PUSH_PAIRS overrides.
-constexpr int kDefaultPushPairs = 0;
-
 static int env_int(const char* name, int fallback) {
   const char* v = getenv(name);
   if (v == nullptr || *v == '\0') return fallback;
   const int x = atoi(v);
   return x > 0 ? x : fallback;
-}
-
-// Like env_int, for knobs where 0 is a setting of its own.
-static int env_int0(const char* name, int fallback) {
-  const char* v = getenv(name);
-  if (v == nullptr || *v == '\0') return fallback;
-  const int x = atoi(v);
-  return x >= 0 ? x : fallback;
 }
 
 // CTA pairs that can be resident at once. A persistent grid never exceeds it: in recv mode the
@@ -36,7 +25,8 @@ static int resident_pairs(bool mx, int threads, int* out) {
   FGA_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return set_error(kUnsupported, "device index %d out of range", dev);
   const int slot = threads <= 32 * kGemmWarps ? 0 : (threads <= 32 * (kGemmWarps + kPusherWarps) ? 1 : 2);
-  int& entry = cached[dev][mx ? 1 : 0][slot];
+  int& slot_ref = cached[dev][mx ? 1 : 0][slot];
+  int entry = __atomic_load_n(&slot_ref, __ATOMIC_RELAXED);
   if (entry == 0) {
     const void* fn = mx ? reinterpret_cast<const void*>(ulysses_gemm_kernel<true>)
                         : reinterpret_cast<const void*>(ulysses_gemm_kernel<false>);
@@ -56,6 +46,7 @@ static int resident_pairs(bool mx, int threads, int* out) {
     FGA_CUDA(cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg));
     if (clusters < 1) return set_error(kCudaError, "no CTA pair of the GEMM kernel fits on this device");
     entry = clusters;
+    __atomic_store_n(&slot_ref, entry, __ATOMIC_RELAXED);
   }
   *out = entry;
   return kSuccess;
@@ -113,6 +104,21 @@ static int choose_k_splits(long long tiles, int k_tiles, int pairs) {
   return forced <= 1 ? 1 : sched::pick_k_splits(tiles, k_tiles, pairs, forced);
 }
 
+// Optional pacing of the recv pushers (FGA_PUSH_LEAD = raster groups they may run ahead of this
+// rank's own GEMM; off by default). The GEMM publishes 1 + the pair tile it has started in
+// `progress`, which is zeroed on the stream in front of the launch (a memset node under capture).
+// Only launches that run both roles are paced: pushers without a GEMM would wait for nothing.
+static int pace_pushers(GemmParams& P, int32_t* progress, cudaStream_t stream) {
+  P.progress = nullptr;
+  P.push_lead = 0;
+  const int lead = env_int("FGA_PUSH_LEAD", 0);
+  if (lead <= 0 || progress == nullptr || P.roles != 3) return kSuccess;
+  FGA_CUDA(cudaMemsetAsync(progress, 0, sizeof(int32_t), stream));
+  P.progress = progress;
+  P.push_lead = lead;
+  return kSuccess;
+}
+
 // Block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 across the pair, N = bn.
 // The scale-byte selectors (bits 4-5 and 29-30) are filled in per K block by the kernel.
 static uint32_t make_idesc_mx(int bn) {
@@ -148,6 +154,7 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
   FGA_REQUIRE(n_segment > 0 && n_segment % (p * 128) == 0,
               "Push segment width must be a multiple of CP * tile N");
   for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push: null peer table %d", s);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push: the bias must be 16-byte aligned");
   const int n = segments * n_segment;
   GemmParams P{};
   P.mode = kPush;
@@ -240,14 +247,13 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   // queue that the GEMM's own loads share).
   P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
-  P.epoch = reinterpret_cast<const long long*>(epoch);
-  P.progress = progress;
-  P.push_lead = env_int("FGA_PUSH_LEAD", 0);
-  P.push_pairs = env_int0("FGA_PUSH_PAIRS", kDefaultPushPairs);
+  (void)epoch;
+  int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
+  if (rc != kSuccess) return rc;
   P.status = status;
   P.timeout_ns = timeout_ns;
   CUtensorMap ta, tb;
-  int rc = encode_operand(&ta, recv, 0, recv_rows, k, k, 128);
+  rc = encode_operand(&ta, recv, 0, recv_rows, k, k, 128);
   if (rc != kSuccess) return rc;
   rc = b_is_kn ? encode_operand(&tb, b, 1, n, k, n, 0) : encode_operand(&tb, b, 0, n, k, k, P.bn / 2);
   if (rc != kSuccess) return rc;
@@ -364,6 +370,7 @@ int fga_gemm_push_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int
   const int n = segments * n_segment;
   FGA_REQUIRE(b_rows_padded >= n && b_rows_padded % 128 == 0, "fga_gemm_push_mx: weight rows must be padded");
   for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_mx: null peer table %d", s);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push_mx: the bias must be 16-byte aligned");
   GemmParams P{};
   P.mode = kPush;
   P.epi = kEpiBf16;
@@ -421,6 +428,7 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   for (int t = 0; t < num_in; ++t)
     FGA_REQUIRE(srcs[t] && reinterpret_cast<uintptr_t>(srcs[t]) % 16 == 0,
                 "fga_gemm_recv_mx: source %d must be a 16-byte aligned device pointer", t);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv_mx: output must be 16-byte aligned");
   GemmParams P{};
   P.mode = kRecv;
   P.epi = kEpiBf16;
@@ -456,10 +464,9 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   // queue that the GEMM's own loads share).
   P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
   if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
-  P.epoch = reinterpret_cast<const long long*>(epoch);
-  P.progress = progress;
-  P.push_lead = env_int("FGA_PUSH_LEAD", 0);
-  P.push_pairs = env_int0("FGA_PUSH_PAIRS", kDefaultPushPairs);
+  (void)epoch;
+  int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
+  if (rc != kSuccess) return rc;
   P.quant_src = static_cast<const uint16_t*>(recv);
   P.quant_q = static_cast<uint8_t*>(mx_recv);
   P.quant_sf = static_cast<uint8_t*>(mx_scale);
@@ -468,7 +475,7 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   P.status = status;
   P.timeout_ns = timeout_ns;
   CUtensorMap ta, tb, tsa, tsb;
-  int rc = encode_mx_operand(&ta, &tsa, mx_recv, mx_scale, recv_rows, k, 128);
+  rc = encode_mx_operand(&ta, &tsa, mx_recv, mx_scale, recv_rows, k, 128);
   if (rc != kSuccess) return rc;
   rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, b_kp, P.bn / 2);
   if (rc != kSuccess) return rc;

@@ -20,8 +20,6 @@
 //
 // Shared memory (220 KiB): local/push run 6 pipeline stages of 32 KiB; recv runs 5 stages and
 // gives the sixth to the pusher warps (4 warps x 2 buffers x 4 KiB); 18 KiB of epilogue staging.
-// A recv launch may set CTA pairs aside that only push (GemmParams::push_pairs): all ten warps of
-// such a CTA run the pusher loop with three-slot rings in the otherwise unused pipeline stages.
 #pragma once
 #include "ptx.cuh"
 #include "common.cuh"
@@ -45,13 +43,9 @@ constexpr int kQuantWarps = 2;          // MXFP8 recv: warps that quantize arriv
 constexpr int kGemmWarps = 6;           // TMA, MMA, 4 epilogue
 constexpr int kPusherWarps = 4;
 constexpr int kPushBufBytes = 4096;     // per pusher warp: two of these
-constexpr int kDedWarps = kGemmWarps + kPusherWarps;  // warps that push in a CTA that only pushes
-constexpr int kDedRing = 3;             // ring slots per warp there (the pipeline stages are free)
 constexpr int kSmemBytes =
     kMaxStages * (kStageBytes + kSfStageBytes) + kStagingBytes + kBarrierBytes + 1024;
 static_assert(kPusherWarps * 2 * kPushBufBytes == kStageBytes, "pusher buffers reuse one stage");
-static_assert(kDedWarps * kDedRing * (kPushBufBytes + 8) <= (kMaxStages - 1) * kStageBytes,
-              "rings of a pushing-only CTA fit below the sixth stage");
 
 enum GemmMode : int { kLocal = 0, kPush = 1, kRecv = 2 };
 enum EpiMode : int { kEpiBf16 = 0, kEpiF32Store = 1, kEpiF32Add = 2 };
@@ -92,10 +86,9 @@ struct GemmParams {
   long long recv_k;                // elements per receive-buffer row
   int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
   int push_warps;                  // pusher warps that take jobs (1..kPusherWarps)
-  const long long* epoch;          // a device word that grows with every invocation (barrier epoch), or null
-  int* progress;                   // highest pair tile (tagged with the epoch) this rank's GEMM has started
+  int* progress;                   // 1 + the highest pair tile this rank's GEMM has started; the launcher
+                                   // zeroes it on the stream before a paced launch
   int push_lead;                   // raster groups the pushers may run ahead of the GEMM (0 = unlimited)
-  int push_pairs;                  // CTA pairs at the end of the grid that only push (0 = every CTA pushes)
   // MXFP8 (E4M3 operands, one E8M0 scale per 32 K elements, K step = 128 elements)
   int acc_stages;                  // TMEM accumulator stages: 2, or 1 when MXFP8 uses BN = 256
   int sfa_kblocks, sfb_kblocks;    // 128-element K blocks per 128-row block in the A / B scale layouts
@@ -210,7 +203,7 @@ __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
 // so the data never passes through registers and remote stores queue in the copy engine.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane, uint32_t buf0,
-                                            uint32_t bar0, bool steady, WaitCtx& w) {
+                                            uint32_t bar0, WaitCtx& w) {
   const int hpr = P.heads_per_rank;
   const int row_bytes = hpr * 256;
   const int sub_rows = kTileM / P.split;
@@ -220,8 +213,7 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
   const int jobs_per_block = P.num_in * P.p * P.split;
   const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
-  const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
-  const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
+  const bool paced = P.push_lead > 0 && P.progress != nullptr;
   uint32_t issued = 0;          // chunks issued by this warp (selects the buffer)
   uint32_t loads[2] = {0, 0};   // completed-load count per buffer (selects the barrier phase)
   auto do_job = [&](long long job) {
@@ -235,7 +227,7 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
       if (need > 0 && lane == 0) {
         const uint64_t t0 = globaltimer_ns();
         uint32_t it = 0;
-        while (ld_relaxed_sys_s32(P.progress) - base < need) {
+        while (ld_relaxed_sys_s32(P.progress) <= need) {
           nanosleep(200);
           if ((++it & 0xff) == 0) {
             if (should_abort(w)) break;
@@ -307,152 +299,16 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   // Two phases (as in fused_gemm_a2a_kernels.py:358-380): every pusher warp works on the first two
   // raster groups, which the GEMM cannot start without; afterwards only `push_warps` warps per CTA
   // continue, enough to stay ahead of the GEMM without saturating the NVLink egress queue that
-  // the GEMM's own loads share. `steady` is false when CTAs that only push take that part over.
+  // the GEMM's own loads share.
   const long long first_jobs = sched::first_phase_jobs(P.m_tiles, P.group_m, P.num_in, P.p, P.split);
   for (long long job = blockIdx.x * kPusherWarps + pusher; job < first_jobs && !w.dead;
        job += static_cast<long long>(gridDim.x) * kPusherWarps)
     do_job(job);
-  if (steady && pusher < P.push_warps)
+  if (pusher < P.push_warps)
     for (long long job = first_jobs + blockIdx.x * P.push_warps + pusher; job < num_jobs && !w.dead;
          job += static_cast<long long>(gridDim.x) * P.push_warps)
       do_job(job);
   if (lane == 0) bulk_wait_all();
-}
-
-// ---------------------------------------------------------------------------------------------
-// The same job loop for a CTA that only pushes (GemmParams::push_pairs): the warp takes jobs
-// job_begin, job_begin + job_stride, ... < job_end and owns a ring of kRing shared buffers (buf0)
-// and mbarriers (bar0), so that the load of the next chunk is in flight while the stores of the
-// current one are issued.
-// ---------------------------------------------------------------------------------------------
-struct PushRing {
-  uint32_t seq = 0;     // chunks started on this ring (selects the slot)
-  uint32_t parity = 0;  // bit b: phase of slot b's next load completion (lane 0's copy is the one used)
-};
-
-template <int kRing>
-__device__ __noinline__ void run_pushers_ring(const GemmParams& P, long long job_begin, long long job_end,
-                                         long long job_stride, int lane, uint32_t buf0, uint32_t bar0,
-                                         PushRing& ring, WaitCtx& w) {
-  static_assert(kRing >= 2 && kRing <= 8, "ring depth");
-  const int hpr = P.heads_per_rank;
-  const int row_bytes = hpr * 256;
-  const int sub_rows = kTileM / P.split;
-  const int upp = P.push_units, rpc = P.push_rows;
-  const int pieces_per_row = hpr / upp;
-  const int chunk_row_bytes = upp * 256;
-  const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
-  const bool paced = P.push_lead > 0 && P.epoch != nullptr && P.progress != nullptr;
-  const int base = paced ? static_cast<int>(*P.epoch & 0x3fff) << 17 : 0;
-  uint32_t seq = ring.seq, parity = ring.parity;
-  for (long long job = job_begin; job < job_end && !w.dead; job += job_stride) {
-    const sched::PushJob j = sched::decode_push_job(job, P.num_in, P.p, P.split, P.rank);
-    const int mi = j.mi, t = j.t, d = j.d, row0 = j.row0;
-    if (paced) {
-      // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
-      // the same schedule, so the peers consume at about this rank's pace; pushing faster only
-      // saturates the NVLink egress queue, behind which the GEMM's own loads then wait.
-      const int need = ((mi >> 1) / P.group_m - P.push_lead) * P.group_m;  // pair tile that must have started
-      if (need > 0 && lane == 0) {
-        const uint64_t t0 = globaltimer_ns();
-        uint32_t it = 0;
-        while (ld_relaxed_sys_s32(P.progress) - base < need) {
-          nanosleep(200);
-          if ((++it & 0xff) == 0) {
-            if (should_abort(w)) break;
-            if (globaltimer_ns() - t0 > w.timeout_ns) {
-              report(w, kErrCounterTimeout, 41, mi);
-              break;
-            }
-          }
-        }
-      }
-      __syncwarp();
-    }
-    const char* src = static_cast<const char*>(P.src[t]) +
-                      (static_cast<long long>(d) * P.src_rows + row0) * row_bytes;
-    char* dst = reinterpret_cast<char*>(P.peer_recv[d]) + static_cast<long long>(row0) * P.recv_k * 2;
-    // Chunk c of the job: rows [r0, r0 + rpc) x head units [u0, u0 + upp); `valid` rows exist in the source.
-    auto geometry = [&](int c, int& r0, int& u0, int& valid) {
-      const sched::PushChunk ch = sched::push_chunk(c, hpr, upp, rpc, P.src_rows, row0);
-      r0 = ch.r0;
-      u0 = ch.u0;
-      valid = ch.valid;
-    };
-    // Claim the chunk's ring slot and start its load; rows beyond the logical count become zeros.
-    auto start = [&](int c) {
-      int r0, u0, valid;
-      geometry(c, r0, u0, valid);
-      const int b = static_cast<int>((seq + c) % kRing);
-      const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
-      // The slot's previous chunk is kRing chunks back; at most kRing - 2 newer store groups have
-      // been committed since, so when no more than that many are unread the slot is free.
-      if (lane == 0) bulk_wait_read<kRing - 2>();
-      __syncwarp();
-      if (lane == 0 && valid > 0) {
-        mbar_arrive_expect_tx(bar, valid * chunk_row_bytes);
-        bulk_load(buf, src + static_cast<long long>(r0) * row_bytes + u0 * 256, valid * chunk_row_bytes, bar);
-      }
-      if (valid < rpc) {
-        for (int o = valid * chunk_row_bytes + lane * 16; o < rpc * chunk_row_bytes; o += 512)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(buf + o), "r"(0u) : "memory");
-        fence_proxy_async_shared();
-      }
-      __syncwarp();
-    };
-    // Wait for the chunk's load and hand its rows to the copy engine.
-    auto finish = [&](int c) {
-      if (lane != 0) return;
-      int r0, u0, valid;
-      geometry(c, r0, u0, valid);
-      const int b = static_cast<int>((seq + c) % kRing);
-      const uint32_t buf = buf0 + b * kPushBufBytes, bar = bar0 + 8 * b;
-      bool ok = true;
-      if (valid > 0) {
-        ok = mbar_wait(bar, (parity >> b) & 1u, w, 40);
-        parity ^= 1u << b;
-      }
-      if (ok) {
-        for (int r = 0; r < rpc; ++r) {
-          char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
-          if (P.num_in == 1) {
-            bulk_store(drow + sched::recv_column(P.rank, hpr, u0, 1, 0) * 2, buf + r * chunk_row_bytes,
-                       chunk_row_bytes);
-          } else {
-            for (int u = 0; u < upp; ++u) {
-              const long long col = sched::recv_column(P.rank, hpr, u0 + u, P.num_in, t);
-              bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
-            }
-          }
-        }
-      }
-      bulk_commit();
-    };
-    start(0);
-    for (int c = 0; c < chunks_per_job; ++c) {
-      if (c + 1 < chunks_per_job) start(c + 1);
-      finish(c);
-    }
-    seq += static_cast<uint32_t>(chunks_per_job);
-    if (lane == 0) {
-      // All of this job's bulk stores have been performed; the release makes them visible to
-      // whoever acquires the counter.
-      bulk_wait_all();
-      fence_proxy_async_all();
-      if (!w.dead) {
-        int* ctr = reinterpret_cast<int*>(P.peer_counters[d]) + mi;
-        red_release_sys_add(ctr, 1);
-      }
-    }
-    w.dead = __shfl_sync(0xffffffffu, w.dead ? 1 : 0, 0) != 0;
-  }
-  if (lane == 0) bulk_wait_all();
-  ring.seq = seq;
-  ring.parity = parity;
-}
-
-__device__ __forceinline__ long long first_phase_jobs(const GemmParams& P) {
-  return sched::first_phase_jobs(P.m_tiles, P.group_m, P.num_in, P.p, P.split);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -611,16 +467,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   const int pairs = gridDim.x >> 1;
   const int total_tiles = P.m_tiles * P.n_tiles;
   const int total_units = total_tiles * max(1, P.k_splits);
-  // recv mode may set the last `push_pairs` CTA pairs aside: they run no GEMM role and all of
-  // their warps push for the whole kernel, so that the copy engine and the memory ports of the
-  // SMs that compute carry GEMM traffic only once the first raster groups are out.
-  const int push_pairs = P.mode == kRecv ? min(P.push_pairs, pairs - 1) : 0;
-  const int gemm_pairs = pairs - push_pairs;
-  const bool dedicated = pair >= gemm_pairs;
-  const bool gemm_role = (P.roles & 1) != 0;
-  const bool gemm_on = gemm_role && !dedicated;
-  const uint32_t ded_bufs = smem_base;  // pushing-only CTA: kDedWarps rings in the unused stages
-  const uint32_t ded_bar0 = smem_base + kDedWarps * kDedRing * kPushBufBytes;
+  const bool gemm_on = (P.roles & 1) != 0;
   const int stages = P.stages;
 
   // A device error recorded by an earlier kernel is sticky: every role starts out aborted, so no
@@ -637,8 +484,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       mbar_init(tempty0 + 8 * i, 8);  // 4 epilogue warps x 2 CTAs
     }
     for (int i = 0; i < 2 * kPusherWarps; ++i) mbar_init(push_bar0 + 8 * i, 1);
-    if (dedicated)
-      for (int i = 0; i < kDedWarps * kDedRing; ++i) mbar_init(ded_bar0 + 8 * i, 1);
     asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_word), "r"(0u) : "memory");
     fence_mbar_init();
   }
@@ -657,24 +502,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
-  if (dedicated && warp < kDedWarps) {
-    // ------------------------------------------------------------------ CTA that only pushes
-    if ((P.roles & 2) != 0) {
-      const long long jobs_per_block = static_cast<long long>(P.num_in) * P.p * P.split;
-      const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
-      const long long first_jobs = first_phase_jobs(P);
-      if (warp >= kGemmWarps) {
-        const int pusher = warp - kGemmWarps;
-        run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, false, w);
-      }
-      const int ded_cta = static_cast<int>(blockIdx.x) - 2 * gemm_pairs;
-      PushRing steady;
-      run_pushers_ring<kDedRing>(P, first_jobs + ded_cta * kDedWarps + warp, num_jobs,
-                            static_cast<long long>(2 * push_pairs) * kDedWarps, lane,
-                            ded_bufs + warp * kDedRing * kPushBufBytes, ded_bar0 + 8 * kDedRing * warp,
-                            steady, w);
-    }
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0 && gemm_on) {
       const uint32_t tx_bytes =
@@ -682,7 +510,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       const int b_half = P.bn >> 1;
       int s = 0;
       uint32_t ph = 0;
-      for (int u = pair; u < total_units && !w.dead; u += gemm_pairs) {
+      for (int u = pair; u < total_units && !w.dead; u += pairs) {
         int t, kt0, kt1, m, n;
         unit_coords(P, u, total_tiles, t, kt0, kt1);
         tile_coords(P, t, m, n);
@@ -693,8 +521,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
           const int blk = m * 2 + static_cast<int>(cta_rank);
           if (!counter_wait(P.counters + blk, P.target, w, 10, blk)) break;
           fence_proxy_async_global();
-          if (P.progress != nullptr && P.epoch != nullptr)
-            atomicMax(P.progress, (static_cast<int>(*P.epoch & 0x3fff) << 17) + m);
+          if (P.push_lead > 0 && P.progress != nullptr) atomicMax(P.progress, m + 1);
         }
         for (int kt = kt0; kt < kt1; ++kt) {
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, w, 11)) break;
@@ -743,7 +570,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       const uint32_t a_step = P.a_mn ? 128u : 2u, b_step = P.b_mn ? 128u : 2u;
       int s = 0, as = 0;
       uint32_t ph = 0, aph = 0;
-      for (int u = pair; u < total_units && !w.dead; u += gemm_pairs) {
+      for (int u = pair; u < total_units && !w.dead; u += pairs) {
         int t, kt0, kt1;
         unit_coords(P, u, total_tiles, t, kt0, kt1);
         if (!mbar_wait(tempty0 + 8 * as, aph ^ 1, w, 20)) break;
@@ -799,7 +626,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
       bool stores_pending = false;
       int as = 0;
       uint32_t aph = 0;
-      for (int u = pair; u < total_units; u += gemm_pairs) {
+      for (int u = pair; u < total_units; u += pairs) {
         int t, kt0, kt1, m, n;
         unit_coords(P, u, total_tiles, t, kt0, kt1);
         tile_coords(P, t, m, n);
@@ -827,14 +654,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kGemmWarps + k
     // ------------------------------------------------------------------ pusher warps (recv mode)
     if (P.mode == kRecv && (P.roles & 2) != 0) {
       const int pusher = warp - kGemmWarps;
-      // With CTAs that only push, the ones that compute stop pushing after the first raster groups.
-      run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher,
-                  push_pairs == 0, w);
+      run_pushers(P, pusher, lane, push_bufs + pusher * 2 * kPushBufBytes, push_bar0 + 16 * pusher, w);
     }
   } else {
     // ------------------------------------------------------------------ quantizer warps (MXFP8 recv)
     if constexpr (kMx) {
-      if (P.mode == kRecv && gemm_role) run_quantizers(P, warp - kGemmWarps - kPusherWarps, lane, w);
+      if (P.mode == kRecv && gemm_on) run_quantizers(P, warp - kGemmWarps - kPusherWarps, lane, w);
     }
   }
 

@@ -32,24 +32,25 @@ int sm_count() {
   static int cached[kMaxDevices];  // 0 = not queried yet
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = __atomic_load_n(&cached[dev], __ATOMIC_RELAXED);  // forward and autograd threads both launch
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    __atomic_store_n(&cached[dev], n, __ATOMIC_RELAXED);
   }
-  return cached[dev];
+  return n;
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 tmap_encoder() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (fn == nullptr) {
+  // Initialised once, thread-safely (function-local static).
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }();
   return fn;
 }
 
@@ -104,8 +105,8 @@ static bool driver_entry(const char* name, Fn& fn) {
 }
 
 static const VmmApi& vmm_api() {
-  static VmmApi api;
-  if (!api.complete) {
+  // Initialised once, thread-safely (function-local static); incomplete when any entry is missing.
+  static const VmmApi api = [] {
     VmmApi a;
     a.complete = driver_entry("cuMemGetAllocationGranularity", a.granularity) &&
                  driver_entry("cuMemCreate", a.create) && driver_entry("cuMemRelease", a.release) &&
@@ -114,8 +115,8 @@ static const VmmApi& vmm_api() {
                  driver_entry("cuMemUnmap", a.unmap) && driver_entry("cuMemSetAccess", a.set_access) &&
                  driver_entry("cuMemExportToShareableHandle", a.export_handle) &&
                  driver_entry("cuMemImportFromShareableHandle", a.import_handle);
-    if (a.complete) api = a;
-  }
+    return a;
+  }();
   return api;
 }
 
@@ -347,6 +348,8 @@ int fga_bias_grad_static(const void* dy, int64_t rows, int width, void* out, int
                          int accumulate, void* stream) {
   FGA_REQUIRE(dy && out && rows >= 1 && width >= 1,
               "Bias reduction requires contiguous BF16 rows and a BF16/FP32 output vector");
+  FGA_REQUIRE((rows + 255) / 256 <= 65535, "fga_bias_grad_static: too many rows (%lld)",
+              static_cast<long long>(rows));
   return launch_bias_grad_static(dy, rows, width, out, out_is_f32, accumulate,
                                  static_cast<cudaStream_t>(stream));
 }

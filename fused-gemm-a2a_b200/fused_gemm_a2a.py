@@ -12,16 +12,20 @@ biases use Megatron's per-head [q; k; v; (gate)] row order. All CP ranks call wi
 same order. Returned activations and gradients own ordinary storage.
 
 The host layer is plain PyTorch plumbing (validation, autograd, buffer views). All device work is
-done by libfga.so through its C ABI: symmetric buffers are cudaMalloc'ed once per geometry and
-mapped into every peer with CUDA IPC handles exchanged once over the CP group; the GEMMs are
-hand-written TMA/tcgen05 kernels whose epilogue (push) or pusher warps (receive) perform the
-all-to-all over NVLink. No kernel is compiled at run time and nothing falls back to the CPU.
+done by libfga.so through its C ABI: symmetric buffers are allocated once per geometry and mapped
+into every peer (driver virtual-memory allocations shared as file descriptors, or cudaMalloc +
+CUDA IPC handles), exchanged once over the CP group; the GEMMs are hand-written TMA/tcgen05
+kernels whose epilogue (push) or pusher warps (receive) perform the all-to-all over NVLink. No
+kernel is compiled at run time and nothing falls back to the CPU.
 
 Layout of this file: memory (slabs of symmetric memory and their peer tables), the per-group
 runtime `_Comm` (barrier, status word, GEMM launches), gradient helpers, the two autograd
 functions, the buffer sets and their active-length views, and the public classes.
 """
+import atexit
 import os
+import signal
+import warnings
 from dataclasses import dataclass, field
 
 import torch
@@ -37,7 +41,8 @@ from fused_gemm_a2a_kernels import (  # noqa: F401  (re-exported: the reference'
     reduce_bias_grad, resize_rank_rows, tile_swizzle, validate_peer_count, validate_tile_n,
 )
 
-__all__ = ['FusedGemmA2AWorkspace', 'FusedQKVProjection', 'FusedOutputProjection']
+__all__ = ['FusedGemmA2AWorkspace', 'FusedQKVProjection', 'FusedOutputProjection',
+           'install_exit_guards', 'hold_buffers_after_failure', 'release_all']
 
 # The reference selects between torch's GEMM + add_ and Megatron's accumulating cuBLAS extension
 # for the BF16 weight gradient (fused_gemm_a2a.py:34-40). Here both settings mean the same thing:
@@ -53,13 +58,24 @@ if WGRAD_BACKEND not in ('torch', 'fused_accum'):
 # device time limit, for row blocks that never arrive.
 CHECK_TOKENS = os.environ.get('FGA_CHECK_TOKENS', '0') == '1'
 
-# How symmetric buffers are allocated and mapped into the peers: 'ipc' = cudaMalloc + CUDA IPC memory
-# handles (the default), 'vmm' = the driver's virtual memory management API with POSIX file
-# descriptors passed over Unix-domain sockets. With 'vmm' every mapping holds a reference to the
-# physical memory, so a rank that exits does not invalidate what its peers still store into.
-SYMM_BACKEND = os.environ.get('FGA_SYMM', 'ipc')
-if SYMM_BACKEND not in ('ipc', 'vmm'):
-    raise ValueError('FGA_SYMM must be ipc or vmm')
+# How symmetric buffers are allocated and mapped into the peers: 'vmm' = the driver's virtual memory
+# management API with POSIX file descriptors passed over Unix-domain sockets, 'ipc' = cudaMalloc +
+# CUDA IPC memory handles. With 'vmm' every mapping holds a reference to the physical memory, so a
+# rank that exits (a crash, an exception on one rank, a SIGTERM from the launcher) does not unmap
+# what its peers still store into; with 'ipc' such stores are GPU memory faults. The default 'auto'
+# tries 'vmm' when a group's runtime is created and, if any rank cannot allocate, export, pass or map
+# the memory, the whole group falls back to 'ipc' together (one warning on rank 0).
+SYMM_BACKEND = os.environ.get('FGA_SYMM', 'auto')
+if SYMM_BACKEND not in ('auto', 'ipc', 'vmm'):
+    raise ValueError('FGA_SYMM must be auto, ipc or vmm')
+
+# Seconds a rank waits for a peer while file descriptors are handed around (FGA_SYMM=vmm / auto).
+DESCRIPTOR_TIMEOUT_S = float(os.environ.get('FGA_DESCRIPTOR_TIMEOUT_S', 60))
+
+# With FGA_CHECK_STATUS_EVERY=N every N-th forward of a group synchronizes and raises when a device
+# wait has expired since the last check (never during graph capture). Off by default (0): the status
+# word is then surfaced without synchronizing, see _Comm.post_status / poll_status.
+CHECK_STATUS_EVERY = int(os.environ.get('FGA_CHECK_STATUS_EVERY', 0))
 
 _ALIGN = 1024        # every region of a slab starts on a 1 KiB boundary
 _HANDLE_BYTES = 64   # size of an exported memory handle (FGA_IPC_HANDLE_BYTES)
@@ -118,46 +134,82 @@ def exchange_handles(group, rank, peers, handle, local_address, open_peer):
     return reachable
 
 
-_socket_serial = iter(range(1 << 62))
-
-
-def exchange_descriptors(group, rank, peers, descriptor):
+def exchange_descriptors(group, rank, peers, descriptor, timeout=None):
     """Hand one open file descriptor of every rank to every other rank of the group (all on this
-    host): each rank listens on a Unix-domain socket in the abstract namespace, the socket names go
-    around with one all-gather, and every rank fetches its peers' descriptors as SCM_RIGHTS
-    messages. Returns P descriptors valid in this process: `descriptor` itself at [rank], received
-    duplicates (which the caller closes) elsewhere."""
+    host). Each rank listens on a Unix-domain socket inside a private directory (mode 0700, so only
+    this user can connect), the socket paths and process ids go around with one all-gather, and every
+    rank fetches its peers' descriptors as SCM_RIGHTS messages. A connection is served only when the
+    kernel reports (SO_PEERCRED) the same user and the process id of a rank of this group; anything
+    else is dropped without using up a peer's turn. Every accept, connect and receive is bounded by
+    `timeout` seconds (default FGA_DESCRIPTOR_TIMEOUT_S), after which RuntimeError is raised instead
+    of waiting forever for a rank that died. Returns P descriptors valid in this process:
+    `descriptor` itself at [rank], received duplicates (which the caller closes) elsewhere."""
+    import shutil
     import socket
+    import struct
+    import tempfile
     import threading
-    name = f'\0fga-{os.getpid()}-{next(_socket_serial)}'
+    import time
+    timeout = DESCRIPTOR_TIMEOUT_S if timeout is None else timeout
+    directory = tempfile.mkdtemp(prefix='fga-')
+    path = os.path.join(directory, 'fd')
     server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
-    server.bind(name)
-    server.listen(max(peers, 1))
-    names = [None] * peers
-    dist.all_gather_object(names, name, group=group)
+    received, failure = [], []
+    try:
+        server.bind(path)
+        server.listen(max(peers, 1))
+        identities = [None] * peers
+        dist.all_gather_object(identities, (path, os.getpid()), group=group)
+        members = {pid for _, pid in identities}
+        credentials = struct.Struct('3i')            # struct ucred: pid, uid, gid
 
-    def serve():
-        for _ in range(peers - 1):
-            connection, _ = server.accept()
-            with connection:
-                socket.send_fds(connection, [b'fd'], [descriptor])
+        def serve():
+            served, deadline = 0, time.monotonic() + timeout
+            try:
+                while served < peers - 1:
+                    server.settimeout(max(0.05, deadline - time.monotonic()))
+                    connection, _ = server.accept()
+                    with connection:
+                        connection.settimeout(timeout)
+                        pid, uid, _ = credentials.unpack(
+                            connection.getsockopt(socket.SOL_SOCKET, socket.SO_PEERCRED, credentials.size))
+                        if uid != os.getuid() or pid not in members:
+                            continue               # not a rank of this group: no descriptor, no turn
+                        socket.send_fds(connection, [b'fd'], [descriptor])
+                        served += 1
+            except OSError as error:               # includes socket.timeout
+                failure.append(error)
 
-    server_thread = threading.Thread(target=serve, daemon=True)
-    server_thread.start()
-    received = []
-    for owner in range(peers):
-        if owner == rank:
-            received.append(descriptor)
-            continue
-        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
-            client.connect(names[owner])
-            _, descriptors, _, _ = socket.recv_fds(client, 16, 1)
-        if len(descriptors) != 1:
-            raise RuntimeError('Descriptor exchange returned a malformed message')
-        received.append(descriptors[0])
-    server_thread.join()
-    server.close()
-    return received
+        server_thread = threading.Thread(target=serve, daemon=True)
+        server_thread.start()
+        try:
+            for owner in range(peers):
+                if owner == rank:
+                    received.append(descriptor)
+                    continue
+                with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
+                    client.settimeout(timeout)
+                    client.connect(identities[owner][0])
+                    message, descriptors, _, _ = socket.recv_fds(client, 16, 1)
+                if len(descriptors) != 1 or message != b'fd':
+                    for extra in descriptors:
+                        os.close(extra)
+                    raise RuntimeError('Descriptor exchange returned a malformed message')
+                received.append(descriptors[0])
+        except OSError as error:
+            failure.append(error)
+        server_thread.join(timeout + 1.0)
+        if server_thread.is_alive() and not failure:
+            failure.append(TimeoutError('a peer never fetched this rank\'s descriptor'))
+        if failure:
+            for owner, got in enumerate(received):
+                if owner != rank:
+                    os.close(got)
+            raise RuntimeError(f'Descriptor exchange failed on rank {rank}: {failure[0]!r}')
+        return received
+    finally:
+        server.close()
+        shutil.rmtree(directory, ignore_errors=True)
 
 
 class _Slab:
@@ -171,7 +223,9 @@ class _Slab:
     def region(self, offset, shape, dtype):
         size = _numel(shape) * _itemsize(dtype)
         tensor = self.bytes[offset:offset + size].view(dtype).view(shape)
-        table = torch.tensor([peer + offset for peer in self.peer_bases], dtype=torch.int64, device=self.device)
+        addresses = tuple(peer + offset for peer in self.peer_bases)
+        table = torch.tensor(addresses, dtype=torch.int64, device=self.device)
+        table.peer_addresses = addresses           # host copy: reading the device table would synchronize
         return tensor, table
 
 
@@ -182,6 +236,64 @@ class _RecvBuffer:
     def __init__(self, recv, peer_recv, counters, peer_counters, epoch):
         self.recv, self.counters, self.epoch = recv, counters, epoch
         self.peer_recv, self.peer_counters = peer_recv, peer_counters
+
+
+# ----------------------------------------------------------------------------------------------
+# Leaving in order
+# ----------------------------------------------------------------------------------------------
+_live_comms = []
+
+
+def _drain():
+    """Wait until this process's GPU work has finished. Every device wait of the kernels is bounded,
+    so this returns; afterwards nothing of this process is still storing into a peer's memory."""
+    for comm in list(_live_comms):
+        try:
+            if comm.device.type == 'cuda':
+                torch.cuda.synchronize(comm.device)
+        except Exception:                          # noqa: BLE001  (interpreter shutdown: nothing left to do)
+            pass
+
+
+def _drain_at_exit(comm):
+    """Register a runtime for the interpreter-exit drain (installed once)."""
+    if not _live_comms:
+        atexit.register(_drain)
+    _live_comms.append(comm)
+
+
+def hold_buffers_after_failure():
+    """For launch scripts: call on a rank that hit an unexpected exception, before it exits. The rank's
+    queued kernels finish; then, if any of its symmetric buffers would disappear with the process
+    (cudaMalloc + IPC backing), it keeps them mapped until the peers' bounded device waits have run
+    out (FGA_TIMEOUT_S + 2 s): by then their status words are set and their later launches return at
+    entry instead of storing into freed memory. With VMM-backed buffers nothing has to be held."""
+    import time
+    _drain()
+    if any(comm.p > 1 and comm.symm_backend != 'vmm' for comm in _live_comms):
+        time.sleep(_k.DEVICE_TIMEOUT_NS / 1e9 + 2.0)
+
+
+def release_all():
+    """Collective, for the normal end of a run: every rank gives back the symmetric buffers of all
+    its groups (see _Comm.release), in creation order, after all ranks have drained their devices."""
+    for comm in list(_Comm._instances.values()):
+        comm.release()
+
+
+def install_exit_guards(signals=(signal.SIGTERM,)):
+    """For launch scripts (call once, from the main thread): on SIGTERM - what torchrun sends to the
+    surviving workers when one rank has died - first let this process's queued GPU work finish,
+    then die by the same signal. Without it the context is torn down under kernels that may be in
+    the middle of remote stores. The interpreter-exit drain is always installed; this adds the
+    signal path, which a library must not take over on its own."""
+    def handler(number, _frame):
+        _drain()
+        signal.signal(number, signal.SIG_DFL)
+        os.kill(os.getpid(), number)
+
+    for number in signals:
+        signal.signal(number, handler)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -220,10 +332,16 @@ class _Comm:
         self.pool = {}
         self.projection_buffers = {}
         self._allocations = []            # (backend, local address, addresses as seen from here, mapped bytes)
+        self._status_host = torch.zeros(4, dtype=torch.int32)    # host mirror of the status word
+        if self.status.is_cuda:
+            self._status_host = self._status_host.pin_memory()
+        self._status_event, self._status_posted, self._forwards = None, False, 0
+        self.symm_backend = SYMM_BACKEND if SYMM_BACKEND != 'auto' else None   # None: decided by the first allocation
         self.flags, self.peer_flags = self.symmetric((self.p,), torch.int64)
         self.epoch = self._words(1)
         torch.cuda.synchronize()
         dist.barrier(self.group)
+        _drain_at_exit(self)
 
     def _words(self, count):
         return torch.zeros(count, dtype=torch.int32, device=self.device)
@@ -231,18 +349,34 @@ class _Comm:
     # -- symmetric memory ------------------------------------------------------------------
     def symmetric_bytes(self, nbytes):
         """Allocate `nbytes` of zeroed device memory, map it into every peer and return
-        (local address, list of P addresses of the same buffer as seen from this rank)."""
-        if SYMM_BACKEND == 'vmm':
-            local, seen, mapped = self._map_everywhere_vmm(nbytes)
+        (local address, list of P addresses of the same buffer as seen from this rank). Collective."""
+        backend = self.symm_backend
+        if backend is None:                       # FGA_SYMM=auto: the group's first allocation decides
+            mapping = self._map_everywhere_vmm(nbytes, required=False)
+            backend = self.symm_backend = 'vmm' if mapping is not None else 'ipc'
+            if mapping is None:
+                if self.rank == 0:
+                    warnings.warn('fused_gemm_a2a: symmetric memory falls back to cudaMalloc + CUDA IPC '
+                                  f'({_native.lib().fga_last_error().decode(errors="replace")}); with it a '
+                                  'rank that exits alone invalidates buffers its peers may still write to')
+                mapping = self._map_everywhere_ipc(nbytes)
+        elif backend == 'vmm':
+            mapping = self._map_everywhere_vmm(nbytes, required=True)
         else:
-            local, seen, mapped = self._map_everywhere_ipc(nbytes)
-        self._allocations.append((SYMM_BACKEND, local, list(seen), mapped))
-        usable = torch.tensor(int(all(address and address % 16 == 0 for address in seen)), device=self.device)
-        if self.p > 1:
-            dist.all_reduce(usable, op=dist.ReduceOp.MIN, group=self.group)
-        if not usable.item():
+            mapping = self._map_everywhere_ipc(nbytes)
+        local, seen, mapped = mapping
+        self._allocations.append((backend, local, list(seen), mapped))
+        if not self._everyone(all(address and address % 16 == 0 for address in seen)):
             raise RuntimeError('Peer buffers must be aligned and GPU-addressable')
         return local, seen
+
+    def _everyone(self, fine):
+        """True when `fine` holds on every rank of the group (one small all-reduce)."""
+        if self.p == 1:
+            return bool(fine)
+        verdict = torch.tensor(int(bool(fine)), device=self.device)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(verdict.item())
 
     def _map_everywhere_ipc(self, nbytes):
         """cudaMalloc + one 64-byte CUDA IPC handle per rank."""
@@ -261,20 +395,28 @@ class _Comm:
 
         return local.value, exchange_handles(self.group, self.rank, self.p, handle.raw, local.value, open_peer), nbytes
 
-    def _map_everywhere_vmm(self, nbytes):
+    def _map_everywhere_vmm(self, nbytes, required):
         """Driver VMM allocation + one POSIX file descriptor per rank; every mapping keeps the
-        physical memory alive."""
+        physical memory alive. Two collective steps, each followed by a group-wide verdict so that
+        all ranks succeed or give up together: allocate and export locally; pass the descriptors
+        around and map the peers' memory. On failure everything this rank mapped is released and
+        the result is None, or RuntimeError when `required`."""
         lib, ct = _native.lib(), _native.ctypes
-        size = lib.fga_symm_vmm_size(nbytes)
-        if size < 0:
-            _native.check(-3)
-        local, descriptor = _native.c_void_p(), ct.c_int(-1)
-        _native.check(lib.fga_symm_alloc_vmm(nbytes, ct.byref(local), ct.byref(descriptor)))
-        seen = [local.value]
+        local, descriptor, size, problem = _native.c_void_p(), ct.c_int(-1), -1, None
         try:
-            if self.p > 1:
-                seen = []
-                for owner, received in enumerate(exchange_descriptors(self.group, self.rank, self.p, descriptor.value)):
+            size = lib.fga_symm_vmm_size(nbytes)
+            if size < 0:
+                _native.check(-3)
+            _native.check(lib.fga_symm_alloc_vmm(nbytes, ct.byref(local), ct.byref(descriptor)))
+        except Exception as error:                 # noqa: BLE001  (the verdict must reach the all-reduce)
+            problem = error
+        seen, opened = [local.value], []          # opened: peers' memory mapped by this rank
+        allocated_everywhere = self._everyone(problem is None)
+        if allocated_everywhere and self.p > 1:
+            seen = []
+            try:
+                for owner, received in enumerate(
+                        exchange_descriptors(self.group, self.rank, self.p, descriptor.value)):
                     if owner == self.rank:
                         seen.append(local.value)
                         continue
@@ -283,10 +425,24 @@ class _Comm:
                         _native.check(lib.fga_symm_open_vmm(received, size, ct.byref(remote)))
                     finally:
                         os.close(received)
+                    opened.append(remote.value)
                     seen.append(remote.value)
-        finally:
+            except Exception as error:             # noqa: BLE001
+                problem = error
+            mapped_everywhere = self._everyone(problem is None)
+        else:
+            mapped_everywhere = allocated_everywhere
+        if descriptor.value >= 0:
             os.close(descriptor.value)
-        return local.value, seen, size
+        if mapped_everywhere:
+            return local.value, seen, size
+        for address in opened:                     # undo the partial work of this rank
+            lib.fga_symm_release_vmm(address, size)
+        if local.value:
+            lib.fga_symm_release_vmm(local.value, size)
+        if required:
+            raise RuntimeError(f'FGA_SYMM=vmm: symmetric memory could not be set up on every rank ({problem!r})')
+        return None
 
     def release(self):
         """Give every symmetric buffer of this group back. Collective: all ranks synchronize their
@@ -309,6 +465,8 @@ class _Comm:
         self.projection_buffers.clear()
         for slot in [slot for slot, comm in type(self)._instances.items() if comm is self]:
             del type(self)._instances[slot]
+        if self in _live_comms:
+            _live_comms.remove(self)
         dist.barrier(self.group)
 
     def _allocate(self, nbytes):
@@ -344,18 +502,58 @@ class _Comm:
         device_barrier(self.flags, self.peer_flags, self.rank, self.p, self.status, bump=bump,
                        counters=counters, epoch=advanced)
 
-    def check_status(self):
-        """Synchronize and raise if any kernel of this group gave up on a bounded wait."""
-        code, where, detail, _ = self.status.tolist()
+    @staticmethod
+    def _raise_for(word):
+        code, where, detail = word[0], word[1], word[2]
         if code:
             reason = _native.DEVICE_ERRORS.get(code, 'unknown device error')
-            raise RuntimeError(f'Fused GEMM/A2A device error {code}: {reason} (where={where}, detail={detail})')
+            raise RuntimeError(f'Fused GEMM/A2A device error {code}: {reason} (where={where}, detail={detail}). '
+                               'Outputs and gradients produced since then are not valid; repair or tear down '
+                               'the CP group, then call clear_status()')
+
+    def check_status(self):
+        """Synchronize and raise if any kernel of this group (or an MXFP8 weight gradient launched
+        outside a group on this device) gave up on a bounded wait."""
+        self._raise_for(self.status.tolist())
+        local = _k._local_status.get(self.device)
+        if local is not None:
+            self._raise_for(local.tolist())
 
     def clear_status(self):
         """Zero the status word once a device error has been dealt with. The word is sticky: while
         it holds a code, barriers and fused GEMMs of this group return at entry without touching any
         peer's memory, because the peer that never answered may have unmapped it."""
         self.status.zero_()
+        self._status_host.zero_()
+        self._status_posted = False
+        local = _k._local_status.get(self.device)
+        if local is not None:
+            local.zero_()
+
+    def post_status(self):
+        """Queue a copy of the status word into pinned host memory behind the work issued so far
+        on the current stream (no synchronization; skipped during graph capture). Called at the end
+        of every backward pass; poll_status() looks at the copy later."""
+        if torch.cuda.is_current_stream_capturing():
+            return
+        if self._status_event is None:
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(self.status, non_blocking=True)
+        self._status_event.record()
+        self._status_posted = True
+
+    def poll_status(self):
+        """Raise if a copy queued by post_status() has arrived and shows a device error; never
+        waits. Called at the start of every forward pass, so a step that ran on after a timed-out
+        wait (its kernels return at entry and leave their outputs unwritten) is reported at the next
+        step at the latest. Graph replays run no Python: call check_status() once per step there."""
+        self._forwards += 1
+        capturing = torch.cuda.is_current_stream_capturing()
+        if CHECK_STATUS_EVERY and not capturing and self._forwards % CHECK_STATUS_EVERY == 0:
+            self.check_status()
+        if self._status_posted and not capturing and self._status_event.query():
+            self._status_posted = False
+            self._raise_for(self._status_host.tolist())
 
     @staticmethod
     def push_split(a, num_in, p):
@@ -373,11 +571,6 @@ class _Comm:
               inputs that this kernel's pusher warps distribute to the peers (aux = [peer receive
               buffers, peer counters]); c [rows, N] is the local output.
         b is [N, K] or, with b_is_kn, [K, N]."""
-        if scales:
-            # The reference passes quantized operands and their scales through this method. Here the
-            # MXFP8 launches are issued by the workspace view (run_push / run_recv), which owns the
-            # quantized copies; this entry point takes BF16 operands only.
-            raise NotImplementedError('_Comm.gemm takes BF16 operands; MXFP8 launches go through the workspace view')
         if mode not in ('push', 'recv'):
             raise ValueError('GEMM mode must be push/recv and tile N must divide output width')
         if not all(t.is_contiguous() for t in (a, b, c)):
@@ -387,6 +580,15 @@ class _Comm:
         logical = rows if src_rows is None else src_rows
         if not 1 <= logical <= rows:
             raise ValueError('Receive source rows must be positive and fit the receive buffer')
+        if scales:
+            # MXFP8 (reference fused_gemm_a2a.py:163, 187-192): a and b are E4M3 payloads written by
+            # mxfp8_quantize, scales = (a's scale bytes, b's); b is always [N, K] then. Quantization
+            # pads b's rows, so the output width comes from the segments (push) or from c (recv).
+            if b_is_kn or len(scales) != 2:
+                raise ValueError('MXFP8 operands are K-major payloads with one scale tensor each')
+            self._gemm_mx(mode, a, b, c, aux, counters, num_in, n_segment, num_segments, list(srcs), padded,
+                          head_dim, bias, logical, scales, roles)
+            return
         if padded < rows or padded % _ROW_TILE or (mode == 'recv' and padded != rows):
             raise ValueError('a_rows must be a tile multiple >= the rows of a, and equal to them in recv mode')
         width = b.shape[1] if b_is_kn else b.shape[0]
@@ -410,6 +612,41 @@ class _Comm:
         else:
             self._launch_recv(a, b, b_is_kn, width, c, aux, counters, list(srcs)[:num_in], logical, roles)
 
+    def _gemm_mx(self, mode, aq, bq, c, aux, counters, num_in, n_segment, num_segments, srcs, a_rows,
+                 head_dim, bias, src_rows, scales, roles):
+        """The MXFP8 launches behind gemm(scales=...). push: aq [pad256(M), Kp] x bq [pad(N), Kp].
+        recv: aq is the local E4M3 copy of the receive buffer that the kernel's quantizer warps
+        fill; the BF16 receive buffer itself is this rank's entry of the peer table aux[0]."""
+        lib, stream = _native.lib(), torch.cuda.current_stream().cuda_stream
+        sa, sb = scales
+        if mode == 'push':
+            width = n_segment * num_segments
+            validate_tile_n('push', MMA_N_OUT_PUSH if num_segments == 1 else MMA_N, width, self.p,
+                            n_segment, num_segments, head_dim)
+            if bias is not None and not (tuple(bias.shape) == (width,) and bias.dtype == torch.bfloat16):
+                raise ValueError('GEMM bias requires push mode and a BF16 vector of output-width entries')
+            tables = _native.ptr_array([table.data_ptr() for table in aux[:num_segments]])
+            _native.check(lib.fga_gemm_push_mx(
+                aq.data_ptr(), sa.data_ptr(), aq.shape[0], aq.shape[1], a_rows, bq.data_ptr(), sb.data_ptr(),
+                bq.shape[0], bias.data_ptr() if bias is not None else 0, num_segments, n_segment, tables,
+                c.shape[0] // self.p, self.rank, self.p, self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
+            return
+        if bias is not None:
+            raise ValueError('GEMM bias requires push mode and a BF16 vector of output-width entries')
+        peer_recv, peer_counters = aux[0], aux[1]
+        rows, k = aq.shape
+        if a_rows != rows or counters.numel() != c.shape[0] // CTA_M:
+            raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
+        addresses = getattr(peer_recv, 'peer_addresses', None)
+        recv_address = addresses[self.rank] if addresses is not None else int(peer_recv[self.rank])
+        sources = _native.ptr_array([int(address) for address in srcs[:num_in]])
+        split = push_split(k, self.p, num_in, PUSH_SPLIT)
+        _native.check(lib.fga_gemm_recv_mx(
+            recv_address, aq.data_ptr(), sa.data_ptr(), rows, k, bq.data_ptr(), sb.data_ptr(), bq.shape[0],
+            bq.shape[1], c.shape[1], c.data_ptr(), peer_recv.data_ptr(), peer_counters.data_ptr(),
+            counters.data_ptr(), sources, num_in, src_rows, split, self.rank, self.p, roles,
+            self._pacing_epoch(), self.progress.data_ptr(), self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
+
     def _launch_push(self, a, a_rows, b, b_is_kn, bias, peer_tables, n_segment, head_rows):
         tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
         _native.check(_native.lib().fga_gemm_push(
@@ -429,8 +666,8 @@ class _Comm:
             _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
 
     def _pacing_epoch(self):
-        """Address of this rank's own barrier flag: a device word that grows with every barrier,
-        which the recv kernel uses to tag its progress word (no clearing between invocations)."""
+        """Address of this rank's own barrier flag, a device word that grows with every barrier.
+        The C ABI keeps the argument for compatibility; the kernels no longer read it."""
         return self.flags.data_ptr() + 8 * self.rank
 
     def recv_gemm(self, a, b, b_is_kn, c, peer_recv, peer_counters, counters, num_in, srcs,
@@ -485,7 +722,9 @@ def _weight_grad(weight, a, b, precision='bf16', status=None):
             raise ValueError('MXFP8 main_grad must match the weight shape and device, '
                              'with contiguous FP32 storage and 16-byte alignment')
         target = main_grad if into_main_grad else torch.empty_like(weight)
-        mxfp8_wgrad(a, b, target, accumulate=into_main_grad)
+        # Bounded-wait reports go to the group's status word when the caller has one.
+        report = {} if status is None else {'status': status}
+        mxfp8_wgrad(a, b, target, accumulate=into_main_grad, **report)
         return _accumulated(weight) if into_main_grad else target
     if status is None:
         if dist.is_initialized():
@@ -555,6 +794,7 @@ class _FusedQKV(torch.autograd.Function):
         dy = workspace.recv[:tokens]
         dw = _weight_grad(module.weight, dy, x, workspace.precision, workspace.comm.status)
         db = _bias_grad(module.bias, dy, module.accumulate_bias_grad) if ctx.has_bias else None
+        workspace.comm.post_status()
         return dx[:tokens], dw, db, None, None
 
 
@@ -592,6 +832,7 @@ class _FusedOutput(torch.autograd.Function):
         db = _bias_grad(module.bias, dy, module.accumulate_bias_grad) if ctx.has_bias else None
         comm.barrier()
         do, = resize_rank_rows(workspace.heads, comm.p, tokens, copy=True)
+        comm.post_status()
         return _as_heads(do, module.head_dim), dw, db, None, None, None
 
 
@@ -647,10 +888,6 @@ class _ProjectionWorkspace:
             self.mx_recv = buffers.mx_recv[:capacity]
             self.mx_scale = buffers.mx_scale[:capacity * self.recv.shape[1] // 32]
 
-    @staticmethod
-    def _stream():
-        return torch.cuda.current_stream().cuda_stream
-
     def run_push(self, a, weight, b_is_kn, segments, bias=None):
         comm = self.comm
         width = weight.shape[1] if b_is_kn else weight.shape[0]
@@ -663,14 +900,8 @@ class _ProjectionWorkspace:
         # reduction axis (reference fused_gemm_a2a.py:439-448).
         aq, sa = mxfp8_quantize(a)
         wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
-        validate_tile_n('push', MMA_N_OUT_PUSH if segments == 1 else MMA_N, width, comm.p,
-                        n_segment, segments, self.head_dim)
-        tables = _native.ptr_array([table.data_ptr() for table in self.peer_heads[:segments]])
-        _native.check(_native.lib().fga_gemm_push_mx(
-            aq.data_ptr(), sa.data_ptr(), aq.shape[0], aq.shape[1], self.capacity, wq.data_ptr(),
-            sb.data_ptr(), wq.shape[0], bias.data_ptr() if bias is not None else 0, segments, n_segment,
-            tables, self.capacity, comm.rank, comm.p, comm.status.data_ptr(), _k.DEVICE_TIMEOUT_NS,
-            self._stream()))
+        comm.gemm('push', aq, wq, False, self.heads[0], self.peer_heads, self.counters, 0, n_segment,
+                  segments, a_rows=self.capacity, head_dim=self.head_dim, bias=bias, scales=(sa, sb))
 
     def begin_recv(self):
         self.comm.barrier(bump=True, epoch=self.epoch, counters=self.counters)
@@ -691,15 +922,9 @@ class _ProjectionWorkspace:
         # MXFP8: only BF16 crosses the links; quantizer warps inside the kernel convert each arrived
         # row block into the local E4M3 copy that the GEMM reads (reference fused_gemm_a2a.py:465-470).
         wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
-        sources = _native.ptr_array([t.data_ptr() for t in inputs])
-        _native.check(_native.lib().fga_gemm_recv_mx(
-            self.recv.data_ptr(), self.mx_recv.data_ptr(), self.mx_scale.data_ptr(), self.capacity,
-            self.recv.shape[1], wq.data_ptr(), sb.data_ptr(), wq.shape[0], wq.shape[1], out.shape[1],
-            out.data_ptr(), self.peer_recv.data_ptr(), self.peer_counters.data_ptr(),
-            self.counters.data_ptr(), sources, len(inputs), src_rows,
-            comm.push_split(self.recv, len(inputs), comm.p), comm.rank, comm.p, roles,
-            comm._pacing_epoch(), comm.progress.data_ptr(), comm.status.data_ptr(),
-            _k.DEVICE_TIMEOUT_NS, self._stream()))
+        comm.gemm('recv', self.mx_recv, wq, False, out, [self.peer_recv, self.peer_counters],
+                  self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
+                  head_dim=self.head_dim, src_rows=src_rows, scales=(self.mx_scale, sb), roles=roles)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -858,6 +1083,7 @@ class FusedQKVProjection(_CallerOwnedProjection):
     def forward(self, x, workspace):
         _check_workspace(workspace, self, x)
         _check(x, (x.shape[0], self.weight.shape[1]), 'x')
+        workspace.comm.poll_status()
         if CHECK_TOKENS:
             _agree_on_tokens(workspace.comm, x.shape[0])
         return _FusedQKV.apply(x, self.weight, self.bias, self, workspace._view(x.shape[0], self.segments))
@@ -883,6 +1109,7 @@ class FusedOutputProjection(_CallerOwnedProjection):
         if o.shape[0] % peers:
             raise ValueError('Token count must be divisible by CP')
         tokens = o.shape[0] // peers
+        workspace.comm.poll_status()
         if CHECK_TOKENS:
             _agree_on_tokens(workspace.comm, tokens)
         return _FusedOutput.apply(o, self.weight, self.bias, self, workspace._view(tokens, 1), tokens)

@@ -248,16 +248,18 @@ def mxfp8_gemm(a, sa, b, sb, out, m, n, status, *, accumulate=False):
     return out
 
 
-def mxfp8_wgrad(dy, x, out, *, accumulate=False):
+def mxfp8_wgrad(dy, x, out, *, accumulate=False, status=None):
     """MXFP8 weight gradient out[N_out, K] (=|+=) dy[T, N_out]^T x[T, K]: both operands are
     requantized from BF16 along the token axis (the new reduction axis; FP8 payloads are never
     transposed) and multiplied by the block-scaled GEMM; FP32 outputs may accumulate in place
-    (reference fused_gemm_a2a_kernels.py:1398-1421)."""
+    (reference fused_gemm_a2a_kernels.py:1398-1421). `status` is the device status word that a
+    bounded wait reports to; without one a per-device word is used, which _Comm.check_status() and
+    clear_status() of any group on that device also cover."""
     if accumulate and out.dtype != torch.float32:
         raise ValueError('MXFP8 gradient accumulation requires FP32 output')
     if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous():
         raise ValueError('MXFP8 weight gradient needs a contiguous BF16 or FP32 output')
     dq, ds = mxfp8_quantize(dy.T)
     xq, xs = mxfp8_quantize(x.T)
-    return mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1], _status_word(out.device),
-                      accumulate=accumulate)
+    return mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1],
+                      _status_word(out.device) if status is None else status, accumulate=accumulate)

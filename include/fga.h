@@ -19,11 +19,16 @@
  *     memory (the peer that did not answer may have exited and unmapped it). The host reads the
  *     word, tears the group down or repairs it, and zeroes the word before it launches again.
  *   - all matrices are row-major; BF16 is passed as 16-bit words.
- *   - tuning variables are read from the environment at every launch: FGA_STAGES, FGA_GROUP_M_PUSH,
- *     FGA_GROUP_M_RECV, FGA_GROUP_M_LOCAL (raster group sizes), FGA_PUSHER_WARPS, FGA_PUSH_LEAD,
- *     FGA_PUSH_PAIRS (recv launches: CTA pairs that only push), FGA_WGRAD_SPLITS (fga_gemm_local with
- *     FP32 output: shares of the reduction axis per tile, a number or "auto"). Unset means the
- *     defaults that were measured; none of them changes results beyond FP32 summation order.
+ *   - pointer alignment: matrix operands, outputs, biases and pusher sources must be 16-byte aligned
+ *     (TMA and 16-byte vector accesses); a launcher that would need an aligned pointer and does not
+ *     get one returns FGA_INVALID_ARGUMENT, or takes a scalar path where one exists
+ *     (fga_copy_rank_rows, fga_bias_grad). No kernel is ever launched on a misaligned operand.
+ *   - tuning variables are read from the environment by the launcher, on the host, at every call:
+ *     FGA_STAGES, FGA_GROUP_M_PUSH, FGA_GROUP_M_RECV, FGA_GROUP_M_LOCAL (raster group sizes),
+ *     FGA_PUSHER_WARPS, FGA_PUSH_LEAD, FGA_WGRAD_SPLITS (fga_gemm_local with FP32 output: shares of the
+ *     reduction axis per tile, a number or "auto"). Unset means the defaults that were measured; none
+ *     of them changes results beyond FP32 summation order. A launch captured into a CUDA graph keeps
+ *     the values it was captured with: changing a variable afterwards does not affect replays.
  */
 #ifndef FGA_H_
 #define FGA_H_
@@ -116,10 +121,10 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
  * in [head][q|k|v|g][128] column order, rows >= src_rows as zeros, and bump peer d's counter of
  * that 128-row block; the GEMM c[recv_rows, n] = recv[recv_rows, k] * b^T consumes a row block
  * once its counter reaches p * num_in * split. roles: bit 0 GEMM, bit 1 pushers (both = 3).
- * epoch / progress (both may be NULL): pacing of the pushers. epoch points at a device word that
- * grows between invocations (the barrier flag of this rank); progress is a caller-owned device
- * int32 in which the GEMM publishes the row tile it has reached, tagged with the epoch so that it
- * never needs clearing; the pushers then stay a bounded number of raster groups ahead of it.
+ * progress (may be NULL): pacing of the pushers, used only with FGA_PUSH_LEAD > 0 and roles == 3. A
+ * caller-owned device int32 that the launcher zeroes on the stream in front of the kernel and in
+ * which the GEMM publishes 1 + the row tile it has reached; the pushers then stay a bounded number
+ * of raster groups ahead of it. epoch is reserved and ignored (pass NULL or any device word).
  * Reference: mode 'recv' with _push_jobs / _push_one
  * (fused_gemm_a2a_kernels.py:291-380, 764-772, 798-804). */
 int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_is_kn, int n,

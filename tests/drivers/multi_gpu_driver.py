@@ -13,7 +13,6 @@ and with it its buffers, alive until the peers' bounded waits have run out.
 import contextlib
 import os
 import sys
-import time
 import traceback
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -24,6 +23,7 @@ for path in (ROOT, os.path.join(ROOT, 'fused-gemm-a2a_b200')):
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
+import fused_gemm_a2a  # noqa: E402
 from fused_gemm_a2a import FusedGemmA2AWorkspace, FusedOutputProjection, FusedQKVProjection  # noqa: E402
 from oracle.ulysses_oracle import UlyssesOracle  # noqa: E402
 
@@ -59,8 +59,7 @@ class Agreement:
             return
         for failure in self.failures:
             print(f'[rank {dist.get_rank()}] FAIL {failure}', flush=True)
-        torch.cuda.synchronize()
-        dist.barrier()
+        fused_gemm_a2a.release_all()       # collective: drain, meet, unmap the peers, free
         dist.destroy_process_group()
         sys.exit(1)
 
@@ -76,6 +75,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device('cuda', local)
     dist.init_process_group('nccl', device_id=dev)
+    fused_gemm_a2a.install_exit_guards()   # SIGTERM from the launcher: finish queued GPU work first
     rank, p = dist.get_rank(), dist.get_world_size()
     hidden, heads = 1024, 8
     d = hidden // heads
@@ -250,8 +250,7 @@ def main():
         verdict.settle(f'graph replay {replay}')
     if rank == 0:
         print(f'PASS cuda graph replay; {checks} eager configurations checked on {p} GPUs', flush=True)
-    torch.cuda.synchronize()
-    dist.barrier()
+    fused_gemm_a2a.release_all()           # collective: drain, meet, unmap the peers, free
     dist.destroy_process_group()
 
 
@@ -266,8 +265,8 @@ if __name__ == '__main__':
         # expired and their sticky error status has stopped further launches from writing here.
         traceback.print_exc()
         try:
-            torch.cuda.synchronize()
+            import fused_gemm_a2a
+            fused_gemm_a2a.hold_buffers_after_failure()   # drain, then wait out the peers' device time limit
         except Exception:
             pass
-        time.sleep(float(os.environ.get('FGA_TIMEOUT_S', '10')) + 2.0)
         os._exit(1)

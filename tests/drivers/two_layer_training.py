@@ -16,7 +16,6 @@ where the ranks agree on the verdict before anybody leaves.
 """
 import os
 import sys
-import time
 import traceback
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -189,6 +188,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device('cuda', local)
     dist.init_process_group('nccl', device_id=dev)
+    import fused_gemm_a2a
+    fused_gemm_a2a.install_exit_guards()   # SIGTERM from the launcher: finish queued GPU work first
     failures, errors = run(dev)
     # Ranks leave together: a rank that exits frees buffers its peers may still store into.
     flag = torch.tensor([len(failures)], dtype=torch.int32, device=dev)
@@ -199,8 +200,7 @@ def main():
         worst = max(e['relative_rms'] for e in errors.values())
         print(f'PASS two layers x two micro-batches on {dist.get_world_size()} GPUs; worst relative RMS {worst:.2e}',
               flush=True)
-    torch.cuda.synchronize()
-    dist.barrier()
+    fused_gemm_a2a.release_all()           # collective: drain, meet, unmap the peers, free
     dist.destroy_process_group()
     sys.exit(1 if flag.item() else 0)
 
@@ -214,8 +214,8 @@ if __name__ == '__main__':
         # Unexpected: keep this rank's buffers mapped until the peers' bounded waits have run out.
         traceback.print_exc()
         try:
-            torch.cuda.synchronize()
+            import fused_gemm_a2a
+            fused_gemm_a2a.hold_buffers_after_failure()   # drain, then wait out the peers' device time limit
         except Exception:
             pass
-        time.sleep(float(os.environ.get('FGA_TIMEOUT_S', '10')) + 2.0)
         os._exit(1)

@@ -161,6 +161,16 @@ class _FakeCuda:
     def current_stream(*_):
         return types.SimpleNamespace(cuda_stream=0)
 
+    class Event:
+        """Host work is done when it returns: a recorded event has always completed."""
+
+        def record(self, *_):
+            return None
+
+        @staticmethod
+        def query():
+            return True
+
 
 class _TorchShim:
     """`torch` as seen from inside the package: the real module except for cuda and device."""
@@ -182,10 +192,11 @@ def _host_tensor(address, nbytes, _device):
 def install(fused, rec):
     """Patch the package for tracing; returns a callable that undoes everything."""
     import _fga_native
-    saved = dict(lib=_fga_native.lib, torch=fused.torch, wrap=fused._wrap)
+    saved = dict(lib=_fga_native.lib, torch=fused.torch, wrap=fused._wrap, backend=fused.SYMM_BACKEND)
     names = ('device_barrier', 'resize_rank_rows', 'reduce_bias_grad', 'bf16_wgrad', 'mxfp8_wgrad', 'mxfp8_quantize')
     saved.update({name: getattr(fused, name) for name in names})
     fake = FakeLib(rec)
+    fused.SYMM_BACKEND = 'ipc'      # the recorder's allocator speaks the 64-byte-handle flavour only
     _fga_native.lib = lambda: fake
     fused.torch = _TorchShim()
     fused._wrap = _host_tensor
@@ -210,7 +221,7 @@ def install(fused, rec):
                 status=rec.resolve(status.data_ptr()), accumulate=bool(accumulate))
         return out
 
-    def mxfp8_wgrad(dy, x, out, *, accumulate=False):
+    def mxfp8_wgrad(dy, x, out, *, accumulate=False, status=None):
         rec.log('mxfp8_wgrad', dy=rec.tensor(dy), x=rec.tensor(x), out=rec.tensor(out), accumulate=bool(accumulate))
         return out
 
@@ -225,7 +236,7 @@ def install(fused, rec):
 
     def undo():
         _fga_native.lib = saved['lib']
-        fused.torch, fused._wrap = saved['torch'], saved['wrap']
+        fused.torch, fused._wrap, fused.SYMM_BACKEND = saved['torch'], saved['wrap'], saved['backend']
         for name in names:
             setattr(fused, name, saved[name])
         fused._Comm._instances.clear()

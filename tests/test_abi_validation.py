@@ -14,8 +14,13 @@ TABLES = (ctypes.c_void_p * 4)(P, P, P, P)
 NS = 1_000_000_000
 
 
-def push(m=300, k=512, a_rows=512, segments=3, n_segment=512, head_rows=512, rank=0, p=1, tables=TABLES):
-    return ('fga_gemm_push', (P, m, k, a_rows, P, 0, None, segments, n_segment, tables, head_rows, rank, p, P, NS, None))
+def push(m=300, k=512, a_rows=512, segments=3, n_segment=512, head_rows=512, rank=0, p=1, tables=TABLES, bias=None):
+    return ('fga_gemm_push', (P, m, k, a_rows, P, 0, bias, segments, n_segment, tables, head_rows, rank, p, P, NS, None))
+
+
+def recv_mx(c=P, roles=3):
+    return ('fga_gemm_recv_mx', (P, P, P, 512, 1536, P, P, 512, 1536, 512, c, P, P, P, TABLES, 3, 300, 2, 0, 1, roles,
+                                 None, None, P, NS, None))
 
 
 def recv(recv_rows=512, k=1536, n=512, num_in=3, src_rows=300, split=2, rank=0, p=1, roles=3, srcs=TABLES):
@@ -36,6 +41,11 @@ CASES = [
     (push(a_rows=1024, head_rows=512), 'tile multiple'),
     (push(n_segment=384, p=2), r'CP \* tile N'),
     (push(n_segment=0), r'CP \* tile N'),
+    (push(bias=P + 2), 'bias must be 16-byte aligned'),
+    (('fga_gemm_push_mx', (P, P, 512, 512, 512, P, P, 1536, P + 8, 3, 512, TABLES, 512, 0, 1, P, NS, None)),
+     'bias must be 16-byte aligned'),
+    (recv_mx(c=P + 4), 'output must be 16-byte aligned'),
+    (recv_mx(roles=0), 'roles'),
     (recv(num_in=2), 'three/four'),
     (recv(recv_rows=300), 'multiple of 256'),
     (recv(src_rows=0), 'Receive source rows'),
@@ -64,6 +74,7 @@ CASES = [
     (('fga_copy_rank_rows', (TABLES, TABLES, 1, 1, 1, 1, 100, P, 128, 0, None)), 'Bias must cover'),
     (('fga_bias_grad', (P, 0, 128, P, 0, 0, P, None)), 'Bias reduction requires'),
     (('fga_bias_grad', (P, 256 * 70000, 128, P, 0, 0, P, None)), 'too many rows'),
+    (('fga_bias_grad_static', (P, 256 * 70000, 8, P, 0, 0, None)), 'too many rows'),
     (('fga_mx_quantize', (P, 100, 100, 3, 5, P, P, 256, 128, None)), '16-byte aligned rows or columns'),
     (('fga_mx_quantize', (P, 100, 100, 100, 1, P, P, 100, 128, None)), 'padded|multiple'),
     (('fga_symm_alloc', (0, ctypes.pointer(ctypes.c_void_p()))), 'fga_symm_alloc'),

@@ -81,10 +81,10 @@ def test_provenance_names_versions_tunables_and_digests(monkeypatch):
     import torch
 
     import bench
-    monkeypatch.setenv('FGA_PUSH_PAIRS', '4')
+    monkeypatch.setenv('FGA_PUSHER_WARPS', '4')
     info = bench.provenance(torch)
     assert info['tunables'] == {k: v for k, v in os.environ.items() if k.startswith(('FGA_', 'FUSED_'))}
-    assert info['tunables']['FGA_PUSH_PAIRS'] == '4'
+    assert info['tunables']['FGA_PUSHER_WARPS'] == '4'
     assert info['torch'] == torch.__version__
     for key in ('libfga_sha256', 'csrc_sha256', 'host_layer_sha256'):
         assert info[key] is None or len(info[key]) == 16

@@ -169,10 +169,10 @@ def test_push_routing_matches_the_oracle_layout(sched, p, hidden, heads, segment
 # ------------------------------------------------------------------------------------ pusher jobs
 @pytest.mark.parametrize('m_tiles,num_in,p,split,group_m', [(64, 3, 8, 2, 4), (64, 1, 8, 2, 4), (2, 3, 2, 4, 4),
                                                             (5, 4, 4, 1, 1), (11, 1, 1, 8, 4), (1, 3, 8, 2, 4)])
-@pytest.mark.parametrize('grid,push_pairs', [(148, 0), (148, 4), (148, 73), (4, 1), (2, 0)])
-def test_both_pusher_schedules_run_every_job_once(sched, m_tiles, num_in, p, split, group_m, grid, push_pairs):
-    """All CTAs x 4 warps take the first two raster groups; then either `push_warps` warps of every
-    CTA or all ten warps of the pushing-only CTAs take the rest. Every job exactly once, for any rank."""
+@pytest.mark.parametrize('grid', [148, 4, 2])
+def test_both_pusher_phases_run_every_job_once(sched, m_tiles, num_in, p, split, group_m, grid):
+    """All CTAs x 4 warps take the first two raster groups; then `push_warps` warps of every CTA
+    take the rest. Every job exactly once, for any rank."""
     total = sched.sched_push_jobs_total(m_tiles, num_in, p, split)
     first = sched.sched_first_phase_jobs(m_tiles, group_m, num_in, p, split)
     assert total == m_tiles * 2 * num_in * p * split
@@ -182,21 +182,13 @@ def test_both_pusher_schedules_run_every_job_once(sched, m_tiles, num_in, p, spl
         for warp in range(4):
             for job in range(cta * 4 + warp, first, grid * 4):
                 runs[job] += 1
-    if push_pairs == 0:
-        for push_warps in (1, 2, 4):
-            again = list(runs)
-            for cta in range(grid):
-                for warp in range(push_warps):
-                    for job in range(first + cta * push_warps + warp, total, grid * push_warps):
-                        again[job] += 1
-            assert again == [1] * total
-    else:
-        gemm_pairs = grid // 2 - push_pairs
-        for cta in range(2 * gemm_pairs, grid):
-            for warp in range(10):
-                for job in range(first + (cta - 2 * gemm_pairs) * 10 + warp, total, 2 * push_pairs * 10):
-                    runs[job] += 1
-        assert runs == [1] * total
+    for push_warps in (1, 2, 4):
+        again = list(runs)
+        for cta in range(grid):
+            for warp in range(push_warps):
+                for job in range(first + cta * push_warps + warp, total, grid * push_warps):
+                    again[job] += 1
+        assert again == [1] * total
     # decoding: a bijection onto (row block, segment, destination, sub-block), destinations rotated by rank
     for rank in range(p):
         decoded = [job_of(sched, job, num_in, p, split, rank) for job in range(total)]
@@ -313,24 +305,16 @@ def test_random_geometries_keep_the_exactly_once_properties(sched):
         jobs = sched.sched_push_jobs_total(m_tiles, num_in, p, split)
         first = sched.sched_first_phase_jobs(m_tiles, group_m, num_in, p, split)
         grid = 2 * rng.randint(1, 74)
-        push_pairs = rng.randint(0, grid // 2 - 1)
         runs = [0] * jobs
         for cta in range(grid):
             for warp in range(4):
                 for job in range(cta * 4 + warp, first, grid * 4):
                     runs[job] += 1
-        if push_pairs:
-            gemm_ctas = grid - 2 * push_pairs
-            for cta in range(gemm_ctas, grid):
-                for warp in range(10):
-                    for job in range(first + (cta - gemm_ctas) * 10 + warp, jobs, 2 * push_pairs * 10):
-                        runs[job] += 1
-        else:
-            warps = rng.randint(1, 4)
-            for cta in range(grid):
-                for warp in range(warps):
-                    for job in range(first + cta * warps + warp, jobs, grid * warps):
-                        runs[job] += 1
+        warps = rng.randint(1, 4)
+        for cta in range(grid):
+            for warp in range(warps):
+                for job in range(first + cta * warps + warp, jobs, grid * warps):
+                    runs[job] += 1
         assert runs == [1] * jobs
 
         hpr, sub_rows = rng.randint(1, 40), 128 // split

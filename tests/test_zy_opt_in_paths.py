@@ -1,12 +1,13 @@
-"""GPU parity of the two opt-in schedules of the GEMM kernel, both off by default:
+"""GPU parity of paths that are selected by environment variables, all off by default:
 
 * FGA_WGRAD_SPLITS: an FP32 weight gradient whose token axis is cut into shares that add into the
   output with bulk reductions;
-* FGA_PUSH_PAIRS: recv launches in which some CTA pairs only push while the others only compute
-  after the first raster groups.
+* FGA_GROUP_M_RECV=1: recv launches with one row tile per raster group, so that most pusher jobs go
+  through the steady phase of the two-phase pusher schedule;
+* the VMM-backed symmetric allocation on one device.
 
-The file sorts after the tests of the default paths on purpose: these schedules are selected by
-environment variables and nothing else in the suite depends on them.
+The file sorts after the tests of the default paths on purpose: nothing else in the suite depends
+on these settings.
 """
 import os
 import sys
@@ -53,16 +54,12 @@ def test_weight_gradient_split_along_tokens(native, monkeypatch, splits, accumul
     assert torch.equal(wide[:, :64], start[:, :64]) and torch.equal(wide[:, 64 + n:], start[:, 64 + n:])
 
 
-@pytest.mark.parametrize('push_pairs', [0, 3, 200])
 @pytest.mark.parametrize('p,hidden,heads,tokens,num_in', [(2, 512, 4, 1100, 3), (4, 1024, 8, 1300, 1)])
-def test_receive_steady_phase_and_pushing_only_ctas(native, monkeypatch, p, hidden, heads, tokens, num_in,
-                                                    push_pairs):
+def test_receive_steady_phase(native, monkeypatch, p, hidden, heads, tokens, num_in):
     """One row tile per raster group: the first phase covers two of the five or six row tiles and
-    the rest goes through the steady phase, on every CTA (0) or on CTA pairs that only push
-    (3; 200 is clamped so that one pair still computes). Ranks are emulated on one GPU: all the
-    pushes of every rank run first, then every rank's GEMM."""
+    the rest goes through the steady phase. Ranks are emulated on one GPU: all the pushes of every
+    rank run first, then every rank's GEMM."""
     monkeypatch.setenv('FGA_GROUP_M_RECV', '1')
-    monkeypatch.setenv('FGA_PUSH_PAIRS', str(push_pairs))
     receive_case(native, p, hidden, heads, tokens, num_in)
 
 
