@@ -7,7 +7,7 @@ import ctypes
 import os
 from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p, POINTER
 
-_HERE = os.path.dirname(os.path.abspath(__file__))
+_HERE = os.path.dirname(os.path.realpath(__file__))
 LIB_PATH = os.environ.get('FGA_LIB') or os.path.join(_HERE, 'libfga.so')  # FGA_LIB: another build of the same ABI
 
 _lib = None

@@ -22,6 +22,17 @@ MMA_TILER_MN = (256, MMA_N)  # rows of a CTA pair, columns routed as one unit
 CLUSTER_MN = (2, 1)
 USE_2CTA = True
 PUSH_SPLIT = int(os.environ.get('FUSED_PUSH_SPLIT', 0))  # 0: about 64 KB per pusher job
+# The reference's other launch parameters, which its benchmark records by name (benchmark/run.py
+# reads them from this module). Here they are properties of the compiled library, listed with the
+# values this build uses; the FGA_* variables of include/fga.h are the knobs that exist.
+CLUSTER_N = 1                # CTAs along N per cluster: no operand is ever multicast
+RASTER_ALONG_M = False       # N varies fastest inside a raster group
+SWIZZLE = 4                  # pair tiles per raster group of a receive GEMM (FGA_GROUP_M_RECV)
+SWIZZLE_PUSH = 16            # and of a push GEMM (FGA_GROUP_M_PUSH)
+PUSHER_WARPS = 4             # pusher warps per CTA during the first two raster groups
+PUSHER_STEADY_WARPS = 2      # afterwards, once most traffic crosses NVLink (FGA_PUSHER_WARPS); 4 for CP <= 2
+PUSHER_CHUNK = 256           # 16-byte units per pusher chunk: one 4 KiB bulk copy through shared memory
+PUSHER_STREAMING = True      # transport bypasses registers and L1 (bulk copies), like the reference's evict-first stores
 DEVICE_TIMEOUT_NS = int(float(os.environ.get('FGA_TIMEOUT_S', 20)) * 1e9)  # bound of device waits
 
 
@@ -263,3 +274,18 @@ def mxfp8_wgrad(dy, x, out, *, accumulate=False, status=None):
     xq, xs = mxfp8_quantize(x.T)
     return mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1],
                       _status_word(out.device) if status is None else status, accumulate=accumulate)
+
+
+class _InlinePtx:
+    """Stands where the reference keeps its JIT-compiled MXFP8 kernels, whose PTX text its benchmark
+    and driver search for `tcgen05.mma` and `block_scale` (benchmark/run.py:366-371). Nothing is
+    compiled at run time here: `__ptx__` is the text of the inline-PTX wrappers that libfga.so is
+    built from, which hold the block-scaled MMA the MXFP8 kernels issue."""
+
+    def __init__(self, path):
+        with open(path) as source:
+            self.__ptx__ = source.read()
+
+
+_PTX_SOURCE = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'csrc', 'ptx.cuh')
+_native_mxfp8_kernels = [_InlinePtx(_PTX_SOURCE)] if os.path.exists(_PTX_SOURCE) else []

@@ -77,11 +77,15 @@ def main():
     dist.init_process_group('nccl', device_id=dev)
     fused_gemm_a2a.install_exit_guards()   # SIGTERM from the launcher: finish queued GPU work first
     rank, p = dist.get_rank(), dist.get_world_size()
-    hidden, heads = 1024, 8
-    d = hidden // heads
     checks = 0
     verdict = Agreement(dev)
-    for gate, with_bias, bias_in_gemm in ((False, False, False), (True, True, False), (False, True, True)):
+    every_length = (300, 129, 1, 512, 255)
+    configurations = [(1024, 8, False, False, False, every_length), (1024, 8, True, True, False, every_length),
+                      (1024, 8, False, True, True, every_length),
+                      # the benchmark configurations' geometries (at CP = 8: 4 and 3 heads per rank), one length each
+                      (4096, 32, False, False, False, (129,)), (3072, 24, True, True, True, (77,))]
+    for hidden, heads, gate, with_bias, bias_in_gemm, lengths in configurations:
+        d = hidden // heads
         segments = 4 if gate else 3
         g = torch.Generator().manual_seed(4321)  # replicated parameters
         wq = (torch.randn(segments * hidden, hidden, generator=g) / 32).to(BF)
@@ -95,7 +99,7 @@ def main():
         qkv = FusedQKVProjection(hidden, heads, weight=wq_d, bias=bq_d, gate=gate, bias_in_gemm=bias_in_gemm)
         proj = FusedOutputProjection(hidden, heads, weight=wo_d, bias=bo_d)
         oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, bias_in_gemm=bias_in_gemm)
-        for tokens in (300, 129, 1, 512, 255):
+        for tokens in lengths:
             g = torch.Generator().manual_seed(1000 * tokens + rank)
             x = torch.randn(tokens, hidden, generator=g).to(BF).to(dev).requires_grad_()
             grads = [torch.randn(p * tokens, heads // p, d, generator=g).to(BF).to(dev) for _ in range(segments)]
@@ -109,7 +113,7 @@ def main():
             all_grads = list(zip(*[gather(t) for t in grads]))       # [rank][segment]
             all_o = gather(o.detach())
             xs, dys = gather(x.detach()), gather(dy)
-            label = f'gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm} tokens={tokens}'
+            label = f'hidden={hidden} gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm} tokens={tokens}'
             with verdict.checks(label):
                 assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
                 # exact transport: the QKV receive buffer still holds this rank's dY, the output
@@ -135,7 +139,8 @@ def main():
             verdict.settle(label)
             checks += 1
         if rank == 0:
-            print(f'PASS gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm}', flush=True)
+            print(f'PASS hidden={hidden} heads={heads} gate={gate} bias={with_bias} bias_in_gemm={bias_in_gemm}',
+                  flush=True)
 
     # MXFP8: only BF16 crosses the links; expected values quantize every GEMM's operands along its
     # reduction axis on the CPU (E4M3 + E8M0/32) and multiply the exact dequantized values
@@ -148,48 +153,52 @@ def main():
     def mm(a, b):
         return torch.from_numpy(mx.mx_matmul(bits(a), bits(b))).to(BF)
 
-    g = torch.Generator().manual_seed(99)
-    wq = (torch.randn(3 * hidden, hidden, generator=g) / 32).to(BF)
-    wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
-    ws = FusedGemmA2AWorkspace(hidden, heads, 600, precision='mxfp8')
-    wq_d, wo_d = wq.to(dev).requires_grad_(), wo.to(dev).requires_grad_()
-    qkv = FusedQKVProjection(hidden, heads, weight=wq_d)
-    proj = FusedOutputProjection(hidden, heads, weight=wo_d)
-    hpr = heads // p
-    for tokens in (300, 129):
-        g = torch.Generator().manual_seed(555 * tokens + rank)
-        x = torch.randn(tokens, hidden, generator=g).to(BF).to(dev).requires_grad_()
-        grads = [torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev) for _ in range(3)]
-        o = torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev).requires_grad_()
-        dy = torch.randn(tokens, hidden, generator=g).to(BF).to(dev)
-        outs = qkv(x, ws)
-        dx, dwq = torch.autograd.grad(outs, [x, wq_d], grads)
-        y = proj(o, ws)
-        do, dwo = torch.autograd.grad(y, [o, wo_d], dy)
-        torch.cuda.synchronize()
-        xs, dys, all_o = gather(x.detach()), gather(dy), gather(o.detach())
-        all_grads = list(zip(*[gather(t) for t in grads]))
-        with verdict.checks(f'mxfp8 tokens={tokens}'):
-            assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
-            plain = UlyssesOracle(p, hidden, heads, 3)
-            for seg in range(3):
-                want = torch.cat([mm(xr, wq).view(tokens, heads, 3, d)[:, rank * hpr:(rank + 1) * hpr, seg]
-                                  for xr in xs])
-                close(outs[seg], want, f'mxfp8 segment {seg}')
-            dyq = plain.qkv_recv_buffer(all_grads, rank)
-            close(dx, mm(dyq, wq.t()), 'mxfp8 dx')
-            close(dwq, mm(dyq.t(), xs[rank].t()), 'mxfp8 dW_qkv')
-            o_seq = plain.out_recv_buffer(all_o, rank)
-            close(y, mm(o_seq, wo), 'mxfp8 y')
-            full_do = torch.cat([mm(dyr, wo.t())[:, rank * hpr * d:(rank + 1) * hpr * d] for dyr in dys])
-            close(do, full_do.view(p * tokens, hpr, d), 'mxfp8 dO')
-            close(dwo, mm(dys[rank].t(), o_seq.t()), 'mxfp8 dW_o')
-        verdict.settle(f'mxfp8 tokens={tokens}')
+    # (hidden 5120 with 40 heads is the MXFP8 benchmark configuration: 5 heads per rank at CP = 8)
+    for hidden, heads, lengths in ((1024, 8, (300, 129)), (5120, 40, (129,))):
+        d, hpr = hidden // heads, heads // p
+        g = torch.Generator().manual_seed(99)
+        wq = (torch.randn(3 * hidden, hidden, generator=g) / 32).to(BF)
+        wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+        ws = FusedGemmA2AWorkspace(hidden, heads, 600, precision='mxfp8')
+        wq_d, wo_d = wq.to(dev).requires_grad_(), wo.to(dev).requires_grad_()
+        qkv = FusedQKVProjection(hidden, heads, weight=wq_d)
+        proj = FusedOutputProjection(hidden, heads, weight=wo_d)
+        for tokens in lengths:
+            g = torch.Generator().manual_seed(555 * tokens + rank)
+            x = torch.randn(tokens, hidden, generator=g).to(BF).to(dev).requires_grad_()
+            grads = [torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev) for _ in range(3)]
+            o = torch.randn(p * tokens, hpr, d, generator=g).to(BF).to(dev).requires_grad_()
+            dy = torch.randn(tokens, hidden, generator=g).to(BF).to(dev)
+            outs = qkv(x, ws)
+            dx, dwq = torch.autograd.grad(outs, [x, wq_d], grads)
+            y = proj(o, ws)
+            do, dwo = torch.autograd.grad(y, [o, wo_d], dy)
+            torch.cuda.synchronize()
+            xs, dys, all_o = gather(x.detach()), gather(dy), gather(o.detach())
+            all_grads = list(zip(*[gather(t) for t in grads]))
+            label = f'mxfp8 hidden={hidden} tokens={tokens}'
+            with verdict.checks(label):
+                assert ws.comm.status.tolist()[0] == 0, f'device status {ws.comm.status.tolist()}'
+                plain = UlyssesOracle(p, hidden, heads, 3)
+                # rows quantize independently: all ranks' tokens go through one product per weight
+                projected = mm(torch.cat(xs), wq).view(p * tokens, heads, 3, d)
+                for seg in range(3):
+                    close(outs[seg], projected[:, rank * hpr:(rank + 1) * hpr, seg], f'mxfp8 segment {seg}')
+                dyq = plain.qkv_recv_buffer(all_grads, rank)
+                close(dx, mm(dyq, wq.t()), 'mxfp8 dx')
+                close(dwq, mm(dyq.t(), xs[rank].t()), 'mxfp8 dW_qkv')
+                o_seq = plain.out_recv_buffer(all_o, rank)
+                close(y, mm(o_seq, wo), 'mxfp8 y')
+                full_do = mm(torch.cat(dys), wo.t())[:, rank * hpr * d:(rank + 1) * hpr * d]
+                close(do, full_do.reshape(p * tokens, hpr, d), 'mxfp8 dO')
+                close(dwo, mm(dys[rank].t(), o_seq.t()), 'mxfp8 dW_o')
+            verdict.settle(label)
     if rank == 0:
         print('PASS mxfp8', flush=True)
 
     # CUDA graph: one captured step replayed with changed inputs
-    tokens, segments = 333, 3
+    hidden, heads, tokens, segments = 1024, 8, 333, 3
+    d = hidden // heads
     ws = FusedGemmA2AWorkspace(hidden, heads, 600)
     sx = torch.zeros(tokens, hidden, dtype=BF, device=dev).requires_grad_()
     so = torch.zeros(p * tokens, heads // p, d, dtype=BF, device=dev).requires_grad_()

@@ -1,7 +1,8 @@
 """The comparison arm of bench.py (`--impl nccl`: cuBLAS GEMMs + an all-to-all per projection) must
 compute the same projections as the fused path it is timed against. Here it runs on two and four
 CPU ranks under gloo in FP32 and is compared with the oracle: same outputs, same gradients, same
-head-side layouts."""
+head-side layouts. The benchmark's own parity gate (validate_step) is exercised on the same data:
+it must accept correct results and name the tensor that is wrong."""
 import os
 import sys
 
@@ -62,6 +63,43 @@ def worker(rank, world, port, queue):
     rdos, rparams = oracle.out_backward(all_o, dys)
     same(do, rdos[rank], 'dO')
     same(dwo, rparams[rank][0], 'dW_o')
+    # The parity gate bench.py runs in front of its timed region accepts these results ...
+    inputs = dict(x=x, grads=grads, o=o, dy=dy)
+    weights = dict(w_seg=w_seg, wo=wo, bq=None, bo=None)
+    results = dict(outs=outs, dx=dx, dw_seg=per_segment, y=y, do=do, dwo=dwo)
+    report, failures = bench.validate_step(torch, dist, rank, world, hidden, heads, inputs, weights, results,
+                                           (1e-4, 1e-4), tile=128)
+    problems += [f'gate rejected correct results: {f}' for f in failures]
+    if len(report) != segments + 1 + 2 * segments + 1 + 1 + 2:
+        problems.append(f'gate checked {sorted(report)}')
+    # ... and names exactly the tensor that is wrong (a QKV weight gradient whose segments are swapped,
+    # an output that belongs to another rank's heads)
+    swapped = torch.cat([per_segment[hidden:2 * hidden], per_segment[:hidden], per_segment[2 * hidden:]])
+    _, failures = bench.validate_step(torch, dist, rank, world, hidden, heads, inputs, weights,
+                                      dict(results, dw_seg=swapped), (1e-4, 1e-4), tile=128)
+    if not failures or not all('qkv_bwd dW segment' in f and 'segment 2' not in f for f in failures):
+        problems.append(f'swapped weight-gradient segments: {failures}')
+    _, failures = bench.validate_step(torch, dist, rank, world, hidden, heads, inputs, weights,
+                                      dict(results, y=y.roll(1, 0)), (1e-4, 1e-4), tile=128)
+    if [f.split(':')[0] for f in failures] != ['out_fwd y']:
+        problems.append(f'shifted y: {failures}')
+    # The reference's own unfused modules (staged copy), when present, through the same adapter the
+    # benchmark times: same results, and the gate accepts them.
+    module = bench.load_reference_modules()
+    if module is not None:
+        ref = bench.ReferenceUnfused(module, torch, hidden, heads, list(w_seg.split(hidden)), wo, None, None, 'cpu',
+                                     torch.float32, False)
+        xr, orr = x.clone().requires_grad_(), o.clone().requires_grad_()
+        r_outs = ref.qkv_forward(xr)
+        r_dx, r_dws = ref.qkv_backward(r_outs, xr, grads)
+        r_y = ref.out_forward(orr)
+        r_do, r_dwo = ref.out_backward(r_y, orr, dy)
+        r_results = dict(outs=r_outs, dx=r_dx, dw_seg=torch.cat(list(r_dws)), y=r_y, do=r_do, dwo=r_dwo)
+        _, failures = bench.validate_step(torch, dist, rank, world, hidden, heads, inputs, weights, r_results,
+                                          (1e-4, 1e-4), tile=128)
+        problems += [f'reference modules: {f}' for f in failures]
+        for name in ('dx', 'dw_seg', 'y', 'do', 'dwo'):
+            same(r_results[name], results[name], f'reference modules vs restated arm: {name}')
     queue.put((rank, problems))
     dist.barrier()
     dist.destroy_process_group()

@@ -166,7 +166,7 @@ def run_rank(hidden, heads, capacity_tokens, token_counts, cases=None):
         undo(meet=completed)     # after a failure the peers are not at the same point: do not wait for them
 
 
-def worker(rank, world, port, queue):
+def worker(rank, world, port, queue, geometry=None):
     for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
         if path not in sys.path:
             sys.path.insert(0, path)
@@ -174,7 +174,12 @@ def worker(rank, world, port, queue):
     dist.init_process_group('gloo', rank=rank, world_size=world)
     torch.set_num_threads(2)
     try:
-        launches = run_rank(hidden=512, heads=4, capacity_tokens=300, token_counts=(300, 129, 1))
+        if geometry is None:
+            launches = run_rank(hidden=512, heads=4, capacity_tokens=300, token_counts=(300, 129, 1))
+        else:
+            hidden, heads, cases = geometry
+            launches = run_rank(hidden=hidden, heads=heads, capacity_tokens=300, token_counts=(129,),
+                                cases=[CASES[index] for index in cases])
         queue.put((rank, 'ok', launches))
     except BaseException as error:   # report and leave at once; the parent stops the peers
         import traceback
@@ -206,6 +211,28 @@ def test_modules_on_simulated_ranks_match_the_oracle(world):
         # at least 3 BF16 cases x 3 token counts x (6 barriers + 4 GEMMs + 2 weight gradients + 2 row copies)
         # plus the MXFP8 cases
         assert detail > 3 * 3 * 14
+
+
+@pytest.mark.parametrize('hidden,heads,cases', [(768, 6, (1, 2)), (1280, 10, (0, 3))])
+def test_three_and_five_heads_per_rank_on_two_simulated_ranks(hidden, heads, cases):
+    """The heads-per-rank counts of the benchmark configurations with 24 and 40 heads at CP = 8
+    (three and five): an odd number of 128-wide head units per rank, so push tiles and pusher chunks
+    do not pair up evenly. BF16 with gate and bias (early and late) for three, BF16 and MXFP8 for five."""
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, 2, 29664 + heads, queue, (hidden, heads, cases))) for r in range(2)]
+    for proc in procs:
+        proc.start()
+    results = []
+    try:
+        for _ in range(2):
+            results.append(queue.get(timeout=600))
+            assert results[-1][1] == 'ok', f'rank {results[-1][0]}: {results[-1][2]}'
+    finally:
+        for proc in procs:
+            proc.join(timeout=5 if results and results[-1][1] != 'ok' else 120)
+            if proc.is_alive():
+                proc.terminate()
 
 
 def mismatch_worker(rank, world, port, queue):

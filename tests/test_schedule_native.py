@@ -133,7 +133,10 @@ class _CodedOracle(UlyssesOracle):
 
 
 @pytest.mark.parametrize('p,hidden,heads,segments', [(1, 512, 4, 3), (2, 512, 4, 3), (4, 1024, 8, 4), (8, 1024, 8, 3),
-                                                     (2, 512, 4, 1), (8, 1024, 8, 1)])
+                                                     (2, 512, 4, 1), (8, 1024, 8, 1),
+                                                     # the benchmark geometries at CP = 8: 4, 3, 5 heads per rank
+                                                     (8, 4096, 32, 3), (8, 3072, 24, 4), (8, 5120, 40, 3),
+                                                     (8, 3072, 24, 1), (8, 5120, 40, 1)])
 def test_push_routing_matches_the_oracle_layout(sched, p, hidden, heads, segments):
     """Every output element of every source rank lands where the oracle's head-side buffers have it.
     The GEMM output of rank r is a table of distinct codes (through a stand-in for the QKV GEMM, or an
@@ -198,7 +201,7 @@ def test_both_pusher_phases_run_every_job_once(sched, m_tiles, num_in, p, split,
 
 
 @pytest.mark.parametrize('hpr,num_in,split', [(4, 3, 2), (4, 1, 2), (16, 3, 4), (32, 1, 8), (1, 4, 1), (3, 3, 1), (20, 1, 4),
-                                              (17, 1, 4)])
+                                              (17, 1, 4), (3, 4, 1), (3, 1, 1), (5, 3, 2), (5, 1, 2), (40, 3, 16)])
 def test_chunks_move_every_byte_of_a_job_once_and_zero_the_missing_rows(sched, hpr, num_in, split):
     sub_rows = 128 // split
     units, rows = chunking(sched, hpr, sub_rows)
