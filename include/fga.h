@@ -75,7 +75,7 @@ int fga_symm_close(void* peer_ptr);
 int fga_symm_free(void* ptr);
 
 /* The same buffers from the driver's virtual memory management API instead of cudaMalloc + CUDA IPC
- * (opt-in; the Python layer selects it with FGA_SYMM=vmm). The physical memory is reference counted
+ * (what the Python layer uses unless FGA_SYMM=ipc or a rank of the group cannot). The physical memory is reference counted
  * by every mapping, the owner's and each importer's, so a rank that exits does not pull the memory
  * out from under peers that are still storing into it. The shareable handle is a POSIX file
  * descriptor, which the host layer passes to the peers over a Unix-domain socket.
