@@ -382,3 +382,82 @@ def test_release_unmaps_every_peer_and_frees_every_buffer_once(backend):
                     wanted.append(('release', address, mapped) if backend == 'vmm' else ('close', address))
             wanted.append(('release', local, mapped) if backend == 'vmm' else ('free', local))
         assert report['released'] == wanted
+
+
+def pipeline_worker(rank, world, port, queue):
+    """Four ranks = two pipeline stages of CP 2 (reference tests/pipeline_setup_driver.py:26-77 with
+    --prepare): every stage creates its workspace on its own CP subgroup first; then stage 0 posts
+    the receive of the token that stage 1 sends back only after its own receive has completed."""
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    import datetime
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    torch.set_num_threads(1)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    from oracle.ulysses_oracle import UlyssesOracle
+    stage_size = world // 2
+    cp_groups = [dist.new_group(list(range(stage_size))), dist.new_group(list(range(stage_size, world)))]
+    pp_forward = [dist.new_group([i, i + stage_size]) for i in range(stage_size)]
+    pp_return = [dist.new_group([i, i + stage_size]) for i in range(stage_size)]
+    stage = rank // stage_size
+    cp = cp_groups[stage]
+    recv_group = pp_return[rank % stage_size] if stage == 0 else pp_forward[rank % stage_size]
+    send_group = pp_forward[rank % stage_size] if stage == 0 else pp_return[rank % stage_size]
+    peer = (rank + stage_size) % world
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    problems = []
+    try:
+        hidden, heads, tokens = 256 * stage_size, 2 * stage_size, 100
+        g = torch.Generator().manual_seed(9 + stage)
+        weight = (torch.randn(4 * hidden, hidden, generator=g) / hidden ** 0.5).to(BF)
+        qkv = fused.FusedQKVProjection(hidden, heads, gate=True, weight=weight)
+        workspace = fused.FusedGemmA2AWorkspace(hidden, heads, 128, cp_group=cp, gate=True)      # --prepare
+        if workspace.comm.p != stage_size or workspace.comm.rank != rank % stage_size:
+            problems.append(f'runtime of the subgroup has p={workspace.comm.p} rank={workspace.comm.rank}')
+        signal, received = torch.tensor([rank + 1.0]), torch.zeros(1)
+        pending = dist.irecv(received, src=peer, group=recv_group)
+        if stage == 1:
+            pending.wait()
+        again = fused.FusedGemmA2AWorkspace(hidden, heads, 128, cp_group=cp, gate=True)          # no communication
+        if again.comm is not workspace.comm or again._buffers[4] is not workspace._buffers[4]:
+            problems.append('a second handle of the same geometry built new buffers')
+        dist.isend(signal, dst=peer, group=send_group).wait()
+        if stage == 0:
+            pending.wait()
+        if received.item() != peer + 1.0:
+            problems.append(f'pipeline token {received.item()}')
+        # and the projection runs on the subgroup: this stage's two ranks against a two-rank oracle
+        x = torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(100 + rank)).to(BF)
+        outs = qkv(x, workspace)
+        xs = [None] * stage_size
+        dist.all_gather_object(xs, x, group=cp)
+        oracle = UlyssesOracle(stage_size, hidden, heads, 4, weight)
+        for name, got, want in zip('qkvg', outs, oracle.qkv_forward(xs)[rank % stage_size]):
+            try:
+                close(got, want, name)
+            except AssertionError as error:
+                problems.append(str(error))
+        queue.put((rank, problems))
+    finally:
+        undo()
+    dist.destroy_process_group()
+
+
+def test_workspaces_on_cp_subgroups_before_posted_pipeline_receives():
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=pipeline_worker, args=(r, 4, 29683, queue)) for r in range(4)]
+    for proc in procs:
+        proc.start()
+    try:
+        results = sorted(queue.get(timeout=300) for _ in range(4))
+    finally:
+        for proc in procs:
+            proc.join(timeout=120)
+            if proc.is_alive():
+                proc.terminate()
+    for rank, problems in results:
+        assert problems == [], f'rank {rank}: {problems}'
