@@ -50,6 +50,8 @@ def _declare(l):
     l.fga_gemm_push.argtypes = [vp, i, i, i, vp, i, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
     l.fga_gemm_recv.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, vp, vp, vp,
                                 c_uint64, vp]
+    l.fga_gemm_push_gqa.argtypes = [vp, i, i, i, vp, vp, i, i, i, pp, i64, i, i, vp, c_uint64, vp]
+    l.fga_gemm_recv_gqa.argtypes = [vp, i, vp, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, i, i, vp, vp, c_uint64, vp]
     l.fga_gemm_local.argtypes = [vp, i, vp, i, i, i, i, i64, i64, vp, i64, i, i, vp, c_uint64, vp]
     l.fga_gemm_local_mx.argtypes = [vp, vp, i64, vp, vp, i64, i, i, i, vp, i64, i, i, vp, c_uint64, vp]
     l.fga_gemm_push_mx.argtypes = [vp, vp, i64, i, i, vp, vp, i64, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
@@ -64,6 +66,7 @@ def _declare(l):
     l.fga_mx_quantize.argtypes = [vp, i64, i, i64, i64, vp, vp, i64, i, vp]
     for name in ('fga_symm_alloc', 'fga_symm_export', 'fga_symm_open', 'fga_symm_close',
                  'fga_symm_free', 'fga_symm_alloc_vmm', 'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
+                 'fga_gemm_push_gqa', 'fga_gemm_recv_gqa',
                  'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
                  'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
                  'fga_mx_quantize'):
@@ -73,7 +76,7 @@ def _declare(l):
 EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 'fga_symm_alloc', 'fga_symm_export',
            'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_symm_vmm_size', 'fga_symm_alloc_vmm',
            'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push',
-           'fga_gemm_recv', 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
+           'fga_gemm_recv', 'fga_gemm_push_gqa', 'fga_gemm_recv_gqa', 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
            'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
            'fga_bias_grad', 'fga_bias_grad_static_capacity_floats', 'fga_bias_grad_static', 'fga_mx_quantize')
 

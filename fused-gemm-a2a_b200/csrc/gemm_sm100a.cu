@@ -134,6 +134,82 @@ static int encode_mx_operand(CUtensorMap* data, CUtensorMap* scales, const void*
   return encode_tmap_2d(scales, sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, blocks, 128, 128, 1, 128, false);
 }
 
+// Push-mode fields shared by the BF16 and MXFP8 launchers and by the uniform and grouped-query head
+// layouts: `n` output columns = p * layout.groups_per_rank groups of group_units 128-wide units.
+static void fill_push(GemmParams& P, int n, const sched::HeadLayout& layout, const int64_t* const* peer_heads,
+                      int kinds, int64_t head_rows, int rank, int p, const void* bias, int32_t* status,
+                      uint64_t timeout_ns) {
+  P.mode = kPush;
+  P.epi = kEpiBf16;
+  P.n_tiles = n / P.bn;
+  P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
+  P.stages = kMaxStages;
+  P.rank = rank;
+  P.p = p;
+  P.bias = static_cast<const uint16_t*>(bias);
+  for (int s = 0; s < 4; ++s)
+    P.peer_heads[s] = reinterpret_cast<const long long*>(peer_heads[s < kinds ? s : 0]);
+  P.layout = layout;
+  P.head_rows = head_rows;
+  P.n_rotate = (P.n_tiles % p == 0) ? rank * (P.n_tiles / p) : 0;
+  P.roles = 1;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+}
+
+// Recv-mode fields shared the same way. Input t (t < num_in) is of kind t; its rows are
+// kind_pitch_units(layout, t) head units wide.
+static void fill_recv(GemmParams& P, int recv_rows, int k, int n, void* c, const sched::HeadLayout& layout,
+                      const int64_t* peer_recv, const int64_t* peer_counters, int32_t* counters,
+                      const void* const* srcs, int num_in, int src_rows, int split, int rank, int p, int roles,
+                      int32_t* status, uint64_t timeout_ns) {
+  P.mode = kRecv;
+  P.epi = kEpiBf16;
+  P.m_tiles = recv_rows / 256;
+  P.n_tiles = n / P.bn;
+  P.group_m = env_int("FGA_GROUP_M_RECV", 4);
+  P.stages = kMaxStages - 1;  // the sixth stage's shared memory holds the pusher buffers
+  P.rank = rank;
+  P.p = p;
+  P.c = c;
+  P.c_pitch = n;
+  P.c_rows = recv_rows;
+  P.layout = layout;
+  P.counters = counters;
+  P.peer_recv = reinterpret_cast<const long long*>(peer_recv);
+  P.peer_counters = reinterpret_cast<const long long*>(peer_counters);
+  for (int t = 0; t < 4; ++t) {
+    const int kind = t < num_in ? t : 0;
+    P.src[t] = srcs[kind];
+    P.in_units[t] = sched::kind_pitch_units(layout, kind);
+    // Pusher chunking: a chunk is `push_rows` rows of `push_units` 256-byte head units, at most
+    // one 4 KiB buffer. Rows wider than a buffer are cut into equal pieces of whole units.
+    sched::push_chunking(P.in_units[t], 128 / split, kPushBufBytes, P.push_units[t], P.push_rows[t]);
+  }
+  P.num_in = num_in;
+  P.src_rows = src_rows;
+  P.split = split;
+  P.recv_k = k;
+  P.roles = roles;
+  // Warps per CTA that keep pushing after the first groups: all of them while at least half of the
+  // traffic stays on this GPU, two once most of it crosses NVLink (more only congest the egress
+  // queue that the GEMM's own loads share).
+  P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
+  if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
+  P.status = status;
+  P.timeout_ns = timeout_ns;
+}
+
+// The grouped-query layout of kv_heads groups over p ranks (q_per_kv query heads per key/value head).
+static sched::HeadLayout grouped_layout(int kv_heads, int q_per_kv, int gate, int p) {
+  sched::HeadLayout l;
+  l.q_units = q_per_kv;
+  l.kv_units = 1;
+  l.gate_units = gate ? q_per_kv : 0;
+  l.groups_per_rank = kv_heads / p;
+  return l;
+}
+
 }  // namespace fga
 
 using namespace fga;
@@ -157,30 +233,14 @@ int fga_gemm_push(const void* a, int m, int k, int a_rows, const void* b, int b_
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push: the bias must be 16-byte aligned");
   const int n = segments * n_segment;
   GemmParams P{};
-  P.mode = kPush;
-  P.epi = kEpiBf16;
   P.bn = (n / 128) % 2 == 0 ? 256 : 128;
   P.m_tiles = a_rows / 256;
-  P.n_tiles = n / P.bn;
   P.k_tiles = (k + kTileK - 1) / kTileK;
-  P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
-  P.stages = kMaxStages;
   P.a_mn = 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
-  P.rank = rank;
-  P.p = p;
-  P.bias = static_cast<const uint16_t*>(bias);
-  for (int s = 0; s < 4; ++s)
-    P.peer_heads[s] = reinterpret_cast<const long long*>(peer_heads[s < segments ? s : 0]);
-  P.segments = segments;
-  P.heads_per_rank = n_segment / p / 128;
-  P.head_pitch = n_segment / p;
-  P.head_rows = head_rows;
-  P.n_rotate = (P.n_tiles % p == 0) ? rank * (P.n_tiles / p) : 0;
-  P.roles = 1;
-  P.status = status;
-  P.timeout_ns = timeout_ns;
+  fill_push(P, n, sched::uniform_layout(segments, n_segment / p / 128), peer_heads, segments, head_rows, rank, p,
+            bias, status, timeout_ns);
   CUtensorMap ta, tb;
   int rc = encode_operand(&ta, a, 0, m, k, k, 128);
   if (rc != kSuccess) return rc;
@@ -211,42 +271,14 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
                 "fga_gemm_recv: source %d must be a 16-byte aligned device pointer", t);
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv: output must be 16-byte aligned");
   GemmParams P{};
-  P.mode = kRecv;
-  P.epi = kEpiBf16;
   P.bn = n % 256 == 0 ? 256 : 128;
-  P.m_tiles = recv_rows / 256;
-  P.n_tiles = n / P.bn;
   P.k_tiles = k / kTileK;
-  P.group_m = env_int("FGA_GROUP_M_RECV", 4);
-  P.stages = kMaxStages - 1;  // the sixth stage's shared memory holds the pusher buffers
-  // Pusher chunking: a chunk is `push_rows` rows of `push_units` 256-byte head units, at most
-  // one 4 KiB buffer. Rows wider than a buffer are cut into equal pieces of whole units.
-  sched::push_chunking(k / (p * num_in * 128), 128 / split, kPushBufBytes, P.push_units, P.push_rows);
   P.a_mn = 0;
   P.b_mn = b_is_kn ? 1 : 0;
   P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
-  P.rank = rank;
-  P.p = p;
-  P.c = c;
-  P.c_pitch = n;
-  P.c_rows = recv_rows;
-  P.segments = 1;
-  P.heads_per_rank = k / (p * num_in * 128);
-  P.counters = counters;
+  fill_recv(P, recv_rows, k, n, c, sched::uniform_layout(num_in, k / (p * num_in * 128)), peer_recv, peer_counters,
+            counters, srcs, num_in, src_rows, split, rank, p, roles, status, timeout_ns);
   P.target = p * num_in * split;
-  P.peer_recv = reinterpret_cast<const long long*>(peer_recv);
-  P.peer_counters = reinterpret_cast<const long long*>(peer_counters);
-  for (int t = 0; t < 4; ++t) P.src[t] = srcs[t < num_in ? t : 0];
-  P.num_in = num_in;
-  P.src_rows = src_rows;
-  P.split = split;
-  P.recv_k = k;
-  P.roles = roles;
-  // Warps per CTA that keep pushing after the first groups: all of them while at least half of the
-  // traffic stays on this GPU, two once most of it crosses NVLink (more only congest the egress
-  // queue that the GEMM's own loads share).
-  P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
-  if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
   (void)epoch;
   int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
   if (rc != kSuccess) return rc;
@@ -256,6 +288,88 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
   rc = encode_operand(&ta, recv, 0, recv_rows, k, k, 128);
   if (rc != kSuccess) return rc;
   rc = b_is_kn ? encode_operand(&tb, b, 1, n, k, n, 0) : encode_operand(&tb, b, 0, n, k, k, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+// ---- grouped-query attention: more query heads than key/value heads -----------------------------
+// Same kernels, with the output columns (push) / receive-buffer columns (recv) grouped per
+// key/value head: [q_g0 .. q_g(r-1); k_g; v_g; (gate_g0 .. gate_g(r-1))], r = q_per_kv.
+
+int fga_gemm_push_gqa(const void* a, int m, int k, int a_rows, const void* b, const void* bias, int kv_heads,
+                      int q_per_kv, int gate, const int64_t* const* peer_heads, int64_t head_rows, int rank,
+                      int p, int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(a && b && peer_heads && status, "fga_gemm_push_gqa: null operand, peer table or status");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_push_gqa: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(kv_heads >= 1 && kv_heads % p == 0 && q_per_kv >= 1 && q_per_kv <= 64,
+              "Key/value heads must split evenly over CP ranks (kv_heads=%d, q_per_kv=%d, p=%d)", kv_heads,
+              q_per_kv, p);
+  FGA_REQUIRE(m >= 1 && k >= 8 && k % 8 == 0, "fga_gemm_push_gqa: m >= 1 and k a multiple of 8");
+  FGA_REQUIRE(a_rows >= m && a_rows % 256 == 0 && a_rows <= head_rows,
+              "a_rows must be a tile multiple >= the rows of a and fit the head-side rank block");
+  const int kinds = gate ? 4 : 3;
+  for (int s = 0; s < kinds; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_gqa: null peer table %d", s);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push_gqa: the bias must be 16-byte aligned");
+  const sched::HeadLayout layout = grouped_layout(kv_heads, q_per_kv, gate, p);
+  const long long units = static_cast<long long>(kv_heads) * sched::group_units(layout);
+  FGA_REQUIRE(units * 128 <= 2147483647LL, "fga_gemm_push_gqa: too many output columns");
+  const int n = static_cast<int>(units) * 128;
+  GemmParams P{};
+  P.bn = units % 2 == 0 ? 256 : 128;
+  P.m_tiles = a_rows / 256;
+  P.k_tiles = (k + kTileK - 1) / kTileK;
+  P.a_mn = 0;
+  P.b_mn = 0;
+  P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
+  fill_push(P, n, layout, peer_heads, kinds, head_rows, rank, p, bias, status, timeout_ns);
+  CUtensorMap ta, tb;
+  int rc = encode_operand(&ta, a, 0, m, k, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_operand(&tb, b, 0, n, k, k, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
+}
+
+int fga_gemm_recv_gqa(const void* recv, int recv_rows, const void* b, int n, void* c, const int64_t* peer_recv,
+                      const int64_t* peer_counters, int32_t* counters, const void* const* srcs, int kv_heads,
+                      int q_per_kv, int gate, int src_rows, int split, int rank, int p, int roles,
+                      int32_t* progress, int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(recv && b && c && peer_recv && peer_counters && counters && srcs && status,
+              "fga_gemm_recv_gqa: null argument");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_recv_gqa: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(kv_heads >= 1 && kv_heads % p == 0 && q_per_kv >= 1 && q_per_kv <= 64,
+              "Key/value heads must split evenly over CP ranks (kv_heads=%d, q_per_kv=%d, p=%d)", kv_heads,
+              q_per_kv, p);
+  FGA_REQUIRE(recv_rows >= 256 && recv_rows % 256 == 0, "fga_gemm_recv_gqa: receive rows must be a multiple of 256");
+  FGA_REQUIRE(src_rows >= 1 && src_rows <= recv_rows,
+              "Receive source rows must be positive and fit the receive buffer");
+  FGA_REQUIRE(n >= 128 && n % 128 == 0, "GEMM mode must be push/recv and tile N must divide output width");
+  FGA_REQUIRE(split >= 1 && 128 % split == 0, "FUSED_PUSH_SPLIT must divide 128");
+  FGA_REQUIRE((roles & 3) != 0 && (roles & ~3) == 0, "fga_gemm_recv_gqa: roles is a mask of 1 (GEMM) and 2 (pushers)");
+  const int num_in = gate ? 4 : 3;
+  for (int t = 0; t < num_in; ++t)
+    FGA_REQUIRE(srcs[t] && reinterpret_cast<uintptr_t>(srcs[t]) % 16 == 0,
+                "fga_gemm_recv_gqa: source %d must be a 16-byte aligned device pointer", t);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv_gqa: output must be 16-byte aligned");
+  const sched::HeadLayout layout = grouped_layout(kv_heads, q_per_kv, gate, p);
+  const long long units = static_cast<long long>(kv_heads) * sched::group_units(layout);
+  FGA_REQUIRE(units * 128 <= 2147483647LL, "fga_gemm_recv_gqa: receive rows too wide");
+  const int k = static_cast<int>(units) * 128;
+  GemmParams P{};
+  P.bn = n % 256 == 0 ? 256 : 128;
+  P.k_tiles = k / kTileK;
+  P.a_mn = 0;
+  P.b_mn = 1;   // the weight is [k, n]: dX = dY * W
+  P.idesc = make_idesc(P.a_mn, P.b_mn, P.bn);
+  fill_recv(P, recv_rows, k, n, c, layout, peer_recv, peer_counters, counters, srcs, num_in, src_rows, split, rank,
+            p, roles, status, timeout_ns);
+  P.target = p * num_in * split;
+  int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
+  if (rc != kSuccess) return rc;
+  CUtensorMap ta, tb;
+  rc = encode_operand(&ta, recv, 0, recv_rows, k, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_operand(&tb, b, 1, n, k, n, 0);
   if (rc != kSuccess) return rc;
   return launch(ta, tb, P, static_cast<cudaStream_t>(stream));
 }
@@ -286,8 +400,6 @@ int fga_gemm_local(const void* a, int a_is_km, const void* b, int b_is_kn, int m
   P.c = c;
   P.c_pitch = ldc;
   P.c_rows = m;
-  P.segments = 1;
-  P.heads_per_rank = 1;
   P.roles = 1;
   P.status = status;
   P.timeout_ns = timeout_ns;
@@ -340,8 +452,6 @@ int fga_gemm_local_mx(const void* aq, const void* sfa, int64_t a_rows_padded, co
   P.c = c;
   P.c_pitch = ldc;
   P.c_rows = m;
-  P.segments = 1;
-  P.heads_per_rank = 1;
   P.roles = 1;
   P.sfa_kblocks = P.sfb_kblocks = kp / 128;
   P.status = status;
@@ -372,30 +482,14 @@ int fga_gemm_push_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int
   for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_mx: null peer table %d", s);
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push_mx: the bias must be 16-byte aligned");
   GemmParams P{};
-  P.mode = kPush;
-  P.epi = kEpiBf16;
   P.bn = ((n / 128) % 2 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
   P.acc_stages = P.bn == 256 ? 1 : 2;
   P.m_tiles = a_rows / 256;
-  P.n_tiles = n / P.bn;
   P.k_tiles = kp / 128;
-  P.group_m = env_int("FGA_GROUP_M_PUSH", 16);
-  P.stages = kMaxStages;
   P.idesc = make_idesc_mx(P.bn);
-  P.rank = rank;
-  P.p = p;
-  P.bias = static_cast<const uint16_t*>(bias);
-  for (int s = 0; s < 4; ++s)
-    P.peer_heads[s] = reinterpret_cast<const long long*>(peer_heads[s < segments ? s : 0]);
-  P.segments = segments;
-  P.heads_per_rank = n_segment / p / 128;
-  P.head_pitch = n_segment / p;
-  P.head_rows = head_rows;
-  P.n_rotate = (P.n_tiles % p == 0) ? rank * (P.n_tiles / p) : 0;
-  P.roles = 1;
+  fill_push(P, n, sched::uniform_layout(segments, n_segment / p / 128), peer_heads, segments, head_rows, rank, p,
+            bias, status, timeout_ns);
   P.sfa_kblocks = P.sfb_kblocks = kp / 128;
-  P.status = status;
-  P.timeout_ns = timeout_ns;
   CUtensorMap ta, tb, tsa, tsb;
   int rc = encode_mx_operand(&ta, &tsa, aq, sfa, a_rows_padded, kp, 128);
   if (rc != kSuccess) return rc;
@@ -430,40 +524,14 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
                 "fga_gemm_recv_mx: source %d must be a 16-byte aligned device pointer", t);
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv_mx: output must be 16-byte aligned");
   GemmParams P{};
-  P.mode = kRecv;
-  P.epi = kEpiBf16;
   P.bn = (n % 256 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
   P.acc_stages = P.bn == 256 ? 1 : 2;
-  P.m_tiles = recv_rows / 256;
-  P.n_tiles = n / P.bn;
   P.k_tiles = k / 128;
-  P.group_m = env_int("FGA_GROUP_M_RECV", 4);
-  P.stages = kMaxStages - 1;
-  sched::push_chunking(k / (p * num_in * 128), 128 / split, kPushBufBytes, P.push_units, P.push_rows);
   P.idesc = make_idesc_mx(P.bn);
-  P.rank = rank;
-  P.p = p;
-  P.c = c;
-  P.c_pitch = n;
-  P.c_rows = recv_rows;
-  P.segments = 1;
-  P.heads_per_rank = k / (p * num_in * 128);
-  P.counters = counters;
+  fill_recv(P, recv_rows, k, n, c, sched::uniform_layout(num_in, k / (p * num_in * 128)), peer_recv, peer_counters,
+            counters, srcs, num_in, src_rows, split, rank, p, roles, status, timeout_ns);
   P.quant_arrivals = p * num_in * split;
   P.target = P.quant_arrivals + 16;
-  P.peer_recv = reinterpret_cast<const long long*>(peer_recv);
-  P.peer_counters = reinterpret_cast<const long long*>(peer_counters);
-  for (int t = 0; t < 4; ++t) P.src[t] = srcs[t < num_in ? t : 0];
-  P.num_in = num_in;
-  P.src_rows = src_rows;
-  P.split = split;
-  P.recv_k = k;
-  P.roles = roles;
-  // Warps per CTA that keep pushing after the first groups: all of them while at least half of the
-  // traffic stays on this GPU, two once most of it crosses NVLink (more only congest the egress
-  // queue that the GEMM's own loads share).
-  P.push_warps = env_int("FGA_PUSHER_WARPS", p <= 2 ? kPusherWarps : 2);
-  if (P.push_warps > kPusherWarps) P.push_warps = kPusherWarps;
   (void)epoch;
   int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
   if (rc != kSuccess) return rc;

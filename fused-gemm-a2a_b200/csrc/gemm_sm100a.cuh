@@ -68,10 +68,9 @@ struct GemmParams {
   int c_rows;         // rows of c that exist; others are not stored
   // push
   const uint16_t* bias;            // BF16 bias indexed by weight row, added in FP32, or null
-  const long long* peer_heads[4];  // device int64[P]: peers' head-side buffer base per segment
-  int segments;                    // 3/4 (QKV/QKVG: weight rows interleaved per head) or 1
-  int heads_per_rank;              // 128-column head tiles owned by each rank
-  long long head_pitch;            // elements per head-side buffer row (H / P)
+  const long long* peer_heads[4];  // device int64[P]: peers' head-side buffer base per kind (q, k, v, gate)
+  sched::HeadLayout layout;        // how the output columns (push) / receive-buffer columns (recv) are
+                                   // grouped into heads and which rank owns which group
   long long head_rows;             // rows of one rank block in the head-side buffers (capacity)
   int n_rotate;                    // N-tile rotation so that ranks start on different peers
   // recv
@@ -79,10 +78,12 @@ struct GemmParams {
   int target;                      // arrivals that complete a row block
   const long long* peer_recv;      // device int64[P]
   const long long* peer_counters;  // device int64[P]
-  const void* src[4];              // head-side inputs [P*src_rows, heads_per_rank*128] BF16
+  const void* src[4];              // head-side inputs [P*src_rows, in_units[t]*128] BF16
   int num_in, src_rows, split;
-  int push_units;                  // 256-byte head units per pusher chunk row (divides heads_per_rank)
-  int push_rows;                   // rows per pusher chunk (1 unless push_units == heads_per_rank)
+  int in_units[4];                 // 128-wide units per row of input t (q and gate: groups_per_rank*q_units,
+                                   // k and v: groups_per_rank)
+  int push_units[4];               // 256-byte units per pusher chunk row of input t (divides in_units[t])
+  int push_rows[4];                // rows per pusher chunk (1 unless push_units[t] == in_units[t])
   long long recv_k;                // elements per receive-buffer row
   int roles;                       // bit 0: GEMM roles run, bit 1: pusher warps run
   int push_warps;                  // pusher warps that take jobs (1..kPusherWarps)
@@ -204,13 +205,7 @@ __device__ __forceinline__ int b_row0_of(const GemmParams& P, int n) {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int lane, uint32_t buf0,
                                             uint32_t bar0, WaitCtx& w) {
-  const int hpr = P.heads_per_rank;
-  const int row_bytes = hpr * 256;
   const int sub_rows = kTileM / P.split;
-  const int upp = P.push_units, rpc = P.push_rows;
-  const int pieces_per_row = hpr / upp;
-  const int chunk_row_bytes = upp * 256;
-  const int chunks_per_job = pieces_per_row == 1 ? sub_rows / rpc : sub_rows * pieces_per_row;
   const int jobs_per_block = P.num_in * P.p * P.split;
   const long long num_jobs = static_cast<long long>(P.m_tiles) * 2 * jobs_per_block;
   const bool paced = P.push_lead > 0 && P.progress != nullptr;
@@ -219,6 +214,13 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
   auto do_job = [&](long long job) {
     const sched::PushJob j = sched::decode_push_job(job, P.num_in, P.p, P.split, P.rank);
     const int mi = j.mi, t = j.t, d = j.d, row0 = j.row0;
+    // Geometry of this input: its rows are in_units[t] head units wide (the same for every input
+    // unless query heads outnumber key/value heads).
+    const int hpr = P.in_units[t];
+    const int row_bytes = hpr * 256;
+    const int upp = P.push_units[t], rpc = P.push_rows[t];
+    const int chunk_row_bytes = upp * 256;
+    const int chunks_per_job = sched::push_chunks_per_job(hpr, upp, rpc, sub_rows);
     if (paced) {
       // Pacing: stay at most push_lead raster groups ahead of this rank's own GEMM. Every rank runs
       // the same schedule, so the peers consume at about this rank's pace; pushing faster only
@@ -270,11 +272,11 @@ __device__ __forceinline__ void run_pushers(const GemmParams& P, int pusher, int
           for (int r = 0; r < rpc; ++r) {
             char* drow = dst + static_cast<long long>(r0 + r) * P.recv_k * 2;
             if (P.num_in == 1) {
-              bulk_store(drow + sched::recv_column(P.rank, hpr, u0, 1, 0) * 2, buf + r * chunk_row_bytes,
+              bulk_store(drow + sched::recv_column(P.rank, P.layout, 0, u0) * 2, buf + r * chunk_row_bytes,
                          chunk_row_bytes);
             } else {
               for (int u = 0; u < upp; ++u) {
-                const long long col = sched::recv_column(P.rank, hpr, u0 + u, P.num_in, t);
+                const long long col = sched::recv_column(P.rank, P.layout, t, u0 + u);
                 bulk_store(drow + col * 2, buf + r * chunk_row_bytes + u * 256, 256);
               }
             }
@@ -371,9 +373,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tmem
     const int col0 = pc * piece_cols;
     char* dst = nullptr;
     if (P.mode == kPush) {
-      const sched::PushRoute route = sched::push_route(b_row0 + col0, P.segments, P.heads_per_rank);
+      const sched::PushRoute route = sched::push_route(b_row0 + col0, P.layout);
       dst = reinterpret_cast<char*>(P.peer_heads[route.segment][route.dest]) +
-            sched::push_element(route, P.rank, P.head_rows, row, P.head_pitch) * 2;
+            sched::push_element(route, P.rank, P.head_rows, row) * 2;
     } else if (row < P.c_rows) {
       dst = static_cast<char*>(P.c) +
             (static_cast<long long>(row) * P.c_pitch + b_row0 + col0) * (bf16_out ? 2 : 4);

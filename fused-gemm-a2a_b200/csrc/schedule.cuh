@@ -55,27 +55,70 @@ FGA_HD int rotated_n(int n, int n_rotate, int n_tiles) {
   return n >= n_tiles ? n - n_tiles : n;
 }
 
-// ---- push routing -----------------------------------------------------------------------------
-// Output column `col` (= weight row, Megatron per-head order [q_h; k_h; v_h; (g_h)] when
-// segments > 1) of a push GEMM belongs to 128-wide unit col/128 = head*segments + segment. The head
-// lives on peer head/heads_per_rank, in that peer's buffer of the segment, at column
-// (head % heads_per_rank)*128 + col%128; the rows of source rank r start at r*head_rows.
-struct PushRoute {
-  int segment, dest, column;
+// ---- head layout --------------------------------------------------------------------------------
+// The output columns of a projection (= its weight rows) are 128-wide units, one per (head, kind).
+// Units come in groups, one group per key/value head: `q_units` query heads, then the key head and
+// the value head (`kv_units` = 1, or 0 for the output projection, which has neither), then
+// `gate_units` gate heads (0 or q_units). With one query head per key/value head this is Megatron's
+// per-head order [q_h; k_h; v_h; (g_h)]; with several it is its grouped-query order
+// [q_g0 .. q_g(r-1); k_g; v_g; (gate_g0 .. gate_g(r-1))]. Every rank owns `groups_per_rank`
+// consecutive groups. Kinds are numbered like the head-side buffers: 0 = q, 1 = k, 2 = v, 3 = gate.
+struct HeadLayout {
+  int q_units, kv_units, gate_units, groups_per_rank;
 };
 
-FGA_HD PushRoute push_route(int col, int segments, int heads_per_rank) {
+FGA_HD HeadLayout uniform_layout(int segments, int heads_per_rank) {
+  HeadLayout l;
+  l.q_units = 1;
+  l.kv_units = segments > 1 ? 1 : 0;
+  l.gate_units = segments == 4 ? 1 : 0;
+  l.groups_per_rank = heads_per_rank;
+  return l;
+}
+
+FGA_HD int group_units(const HeadLayout& l) { return l.q_units + 2 * l.kv_units + l.gate_units; }
+
+// Units of kind `kind` per group, and where they start inside the group.
+FGA_HD int kind_units(const HeadLayout& l, int kind) {
+  return kind == 0 ? l.q_units : (kind == 3 ? l.gate_units : l.kv_units);
+}
+FGA_HD int kind_offset(const HeadLayout& l, int kind) {
+  return kind == 0 ? 0 : (kind == 1 ? l.q_units : (kind == 2 ? l.q_units + l.kv_units : l.q_units + 2 * l.kv_units));
+}
+// 128-wide units per row of one rank's head-side buffer of that kind (its row pitch in units).
+FGA_HD int kind_pitch_units(const HeadLayout& l, int kind) { return l.groups_per_rank * kind_units(l, kind); }
+
+// ---- push routing -----------------------------------------------------------------------------
+// Output column `col` of a push GEMM belongs to unit col/128 = group*group_units + position. The
+// group lives on peer group/groups_per_rank, in that peer's buffer of the unit's kind, whose rows are
+// `pitch` elements long, at column ((group % groups_per_rank)*kind_units + index in kind)*128 +
+// col%128; the rows of source rank r start at r*head_rows.
+struct PushRoute {
+  int segment, dest, column, pitch;
+};
+
+FGA_HD PushRoute push_route(int col, const HeadLayout& l) {
   const int unit = col >> 7;
-  const int head = unit / segments;
+  const int per_group = group_units(l);
+  const int group = unit / per_group;
+  const int position = unit - group * per_group;
   PushRoute r;
-  r.segment = unit - head * segments;
-  r.dest = head / heads_per_rank;
-  r.column = (head - r.dest * heads_per_rank) * 128 + (col & 127);
+  r.segment = position < l.q_units ? 0
+              : (position < l.q_units + l.kv_units ? 1 : (position < l.q_units + 2 * l.kv_units ? 2 : 3));
+  const int within = position - kind_offset(l, r.segment);
+  const int per_kind = kind_units(l, r.segment);
+  r.dest = group / l.groups_per_rank;
+  r.column = ((group - r.dest * l.groups_per_rank) * per_kind + within) * 128 + (col & 127);
+  r.pitch = l.groups_per_rank * per_kind * 128;
   return r;
 }
 
-FGA_HD long long push_element(const PushRoute& r, int rank, long long head_rows, int row, long long head_pitch) {
-  return (static_cast<long long>(rank) * head_rows + row) * head_pitch + r.column;
+FGA_HD PushRoute push_route(int col, int segments, int heads_per_rank) {
+  return push_route(col, uniform_layout(segments, heads_per_rank));
+}
+
+FGA_HD long long push_element(const PushRoute& r, int rank, long long head_rows, int row) {
+  return (static_cast<long long>(rank) * head_rows + row) * r.pitch + r.column;
 }
 
 // ---- pusher jobs (recv mode) --------------------------------------------------------------------
@@ -151,10 +194,18 @@ FGA_HD void push_chunking(int heads_per_rank, int sub_rows, int buffer_bytes, in
     while (rows * 2 * units * 256 <= buffer_bytes && rows * 2 <= sub_rows) rows *= 2;
 }
 
-// First BF16 column, in the receive buffer, of head unit `unit` of input segment t pushed by `rank`:
-// the receive buffer is in weight-row order [head][q|k|v|g][128].
+// First BF16 column, in the receive buffer, of unit `unit` (0 .. kind_pitch_units - 1) of the input of
+// kind `kind` pushed by `rank`: the receive buffer is in weight-row order, group after group.
+FGA_HD long long recv_column(int rank, const HeadLayout& l, int kind, int unit) {
+  const int per_kind = kind_units(l, kind);
+  const int group_local = unit / per_kind;
+  const int within = unit - group_local * per_kind;
+  const long long group = static_cast<long long>(rank) * l.groups_per_rank + group_local;
+  return (group * group_units(l) + kind_offset(l, kind) + within) * 128;
+}
+
 FGA_HD long long recv_column(int rank, int heads_per_rank, int unit, int num_in, int t) {
-  return (static_cast<long long>(rank * heads_per_rank + unit) * num_in + t) * 128;
+  return recv_column(rank, uniform_layout(num_in, heads_per_rank), t, unit);
 }
 
 // ---- K shares of an FP32 gradient GEMM ----------------------------------------------------------

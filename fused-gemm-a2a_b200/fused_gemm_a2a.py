@@ -647,6 +647,36 @@ class _Comm:
             counters.data_ptr(), sources, num_in, src_rows, split, self.rank, self.p, roles,
             self._pacing_epoch(), self.progress.data_ptr(), self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
 
+    def push_gqa(self, a, a_rows, weight, bias, peer_tables, layout, head_rows):
+        """QKV forward with more query heads than key/value heads: `weight` rows (and `bias`) are grouped
+        per key/value head, layout = (kv_heads, q_per_kv, gate); one head-side buffer per kind
+        (q, k, v(, gate)), the k and v buffers 1/q_per_kv as wide as the q buffer."""
+        kv_heads, q_per_kv, gate = layout
+        if not (a.is_contiguous() and weight.is_contiguous()):
+            raise ValueError('Fused kernels need contiguous tensors')
+        if len(peer_tables) != (4 if gate else 3) or not all(len(table) == self.p for table in peer_tables):
+            raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
+        tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
+        _native.check(_native.lib().fga_gemm_push_gqa(
+            a.data_ptr(), a.shape[0], a.shape[1], a_rows, weight.data_ptr(), bias.data_ptr() if bias is not None else 0,
+            kv_heads, q_per_kv, int(gate), tables, head_rows, self.rank, self.p, self.status.data_ptr(),
+            _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+
+    def recv_gqa(self, recv, weight, out, peer_recv, peer_counters, counters, inputs, src_rows, layout, roles=3):
+        """QKV dgrad for the same layout: `inputs` are the head-side gradients of q, k, v(, gate), whose
+        rows are of different widths; `weight` is [rows of the grouped layout, H]."""
+        kv_heads, q_per_kv, gate = layout
+        if counters.numel() != out.shape[0] // CTA_M or recv.shape[0] != out.shape[0]:
+            raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
+        hidden = weight.shape[1]
+        split = push_split(len(inputs) * hidden, self.p, len(inputs), PUSH_SPLIT)   # sized by the widest input
+        sources = _native.ptr_array([t.data_ptr() for t in inputs])
+        _native.check(_native.lib().fga_gemm_recv_gqa(
+            recv.data_ptr(), recv.shape[0], weight.data_ptr(), out.shape[1], out.data_ptr(), peer_recv.data_ptr(),
+            peer_counters.data_ptr(), counters.data_ptr(), sources, kv_heads, q_per_kv, int(gate), src_rows, split,
+            self.rank, self.p, roles, self.progress.data_ptr(), self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS,
+            torch.cuda.current_stream().cuda_stream))
+
     def _launch_push(self, a, a_rows, b, b_is_kn, bias, peer_tables, n_segment, head_rows):
         tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
         _native.check(_native.lib().fga_gemm_push(
@@ -759,6 +789,36 @@ def _as_heads(matrix, head_dim):
     return matrix.view(-1, matrix.shape[1] // head_dim, head_dim)
 
 
+def _kind_units(layout):
+    """(first unit, units) of q, k, v(, gate) inside one key/value group of a grouped layout."""
+    _, q_per_kv, gate = layout
+    return [(0, q_per_kv), (q_per_kv, 1), (q_per_kv + 1, 1)] + ([(q_per_kv + 2, q_per_kv)] if gate else [])
+
+
+def _own_grouped(workspace, comm, tokens, late_bias, head_dim):
+    """Ownership copy of the grouped-query head buffers: q (and gate) are wider than k and v, so the
+    buffers are copied per width class; a late bias is first gathered, per kind, into the contiguous
+    order of this rank's heads of that kind (a few kilobytes), which the copy kernel then adds."""
+    kv_heads, q_per_kv, gate = workspace.layout
+    kinds = _kind_units(workspace.layout)
+    groups = kv_heads // comm.p
+    if late_bias is None:
+        wide = [0] + ([3] if gate else [])
+        owned = {}
+        for members in (wide, [1, 2]):
+            copies = resize_rank_rows([workspace.heads[kind] for kind in members], comm.p, tokens, copy=True)
+            owned.update(zip(members, copies))
+        return [owned[kind] for kind in range(len(kinds))]
+    per_group = kinds[-1][0] + kinds[-1][1]
+    grouped = late_bias.view(kv_heads, per_group, head_dim)[comm.rank * groups:(comm.rank + 1) * groups]
+    owned = []
+    for kind, (first, units) in enumerate(kinds):
+        mine = grouped[:, first:first + units].reshape(-1)
+        owned.append(resize_rank_rows([workspace.heads[kind]], comm.p, tokens, copy=True, bias=mine,
+                                      head_dim=head_dim, head_offset=0)[0])
+    return owned
+
+
 class _FusedQKV(torch.autograd.Function):
     """x [M, H] -> q, k, v(, gate) each [P*M, N/P, D] (reference fused_gemm_a2a.py:312-353)."""
 
@@ -775,9 +835,12 @@ class _FusedQKV(torch.autograd.Function):
         ctx.save_for_backward(x, weight, *(() if bias is None else (bias,)))
         # One pass strips the tile padding, applies a late bias and gives the caller storage of its
         # own: the shared buffers are overwritten by the next call of this geometry.
-        owned = resize_rank_rows(workspace.heads, comm.p, x.shape[0], copy=True, bias=late_bias,
-                                 head_dim=module.head_dim,
-                                 head_offset=comm.rank * module.num_heads // comm.p)
+        if workspace.layout is None:
+            owned = resize_rank_rows(workspace.heads, comm.p, x.shape[0], copy=True, bias=late_bias,
+                                     head_dim=module.head_dim,
+                                     head_offset=comm.rank * module.num_heads // comm.p)
+        else:
+            owned = _own_grouped(workspace, comm, x.shape[0], late_bias, module.head_dim)
         return tuple(_as_heads(t, module.head_dim) for t in owned)
 
     @staticmethod
@@ -844,14 +907,19 @@ class _ProjectionBuffers:
     head-side buffers [P*capacity, H/P], a receive buffer [capacity, segments*H] and its counters,
     all carved from one symmetric slab (reference fused_gemm_a2a.py:395-421)."""
 
-    def __init__(self, comm, capacity, hidden_size, head_dim, segments):
+    def __init__(self, comm, capacity, hidden_size, head_dim, segments, kv_hidden=None):
         self.comm, self.capacity, self.head_dim = comm, capacity, head_dim
         self.workspaces = {}              # active-length views by (capacity, precision)
         self.mx_recv = self.mx_scale = None
+        # Grouped-query attention (kv_hidden < hidden_size): the k and v buffers are narrower than the
+        # q (and gate) buffers, and the receive buffer is as wide as all kinds together.
+        grouped = kv_hidden is not None and kv_hidden != hidden_size and segments > 1
+        self.layout = (kv_hidden // head_dim, hidden_size // kv_hidden, segments == 4) if grouped else None
+        widths = [kv_hidden if grouped and index in (1, 2) else hidden_size for index in range(segments)]
         head_names = [f'head{index}' for index in range(segments)]
-        head_shape = (comm.p * capacity, hidden_size // comm.p)
-        regions = comm.slab([(name, head_shape, torch.bfloat16) for name in head_names] + [
-            ('recv', (capacity, segments * hidden_size), torch.bfloat16),
+        regions = comm.slab([(name, (comm.p * capacity, width // comm.p), torch.bfloat16)
+                             for name, width in zip(head_names, widths)] + [
+            ('recv', (capacity, sum(widths)), torch.bfloat16),
             ('counters', (capacity // CTA_M,), torch.int32)])
         self.heads, self.peer_heads = map(list, zip(*(regions[name] for name in head_names)))
         self.recv, self.peer_recv = regions['recv']
@@ -878,7 +946,7 @@ class _ProjectionWorkspace:
     def __init__(self, buffers, capacity, precision):
         comm = buffers.comm
         self.comm, self.capacity, self.precision = comm, capacity, precision
-        self.head_dim, self.epoch = buffers.head_dim, buffers.epoch
+        self.head_dim, self.epoch, self.layout = buffers.head_dim, buffers.epoch, buffers.layout
         blocks = capacity // CTA_M
         self.heads = [head[:comm.p * capacity] for head in buffers.heads]
         self.recv, self.counters = buffers.recv[:capacity], buffers.counters[:blocks]
@@ -890,6 +958,11 @@ class _ProjectionWorkspace:
 
     def run_push(self, a, weight, b_is_kn, segments, bias=None):
         comm = self.comm
+        if self.layout is not None and segments > 1:
+            if b_is_kn:
+                raise ValueError('The grouped-query push takes the weight as [rows, K]')
+            comm.push_gqa(a, self.capacity, weight, bias, self.peer_heads, self.layout, self.capacity)
+            return
         width = weight.shape[1] if b_is_kn else weight.shape[0]
         n_segment = width // segments
         if self.precision != 'mxfp8':
@@ -909,11 +982,19 @@ class _ProjectionWorkspace:
     def run_recv(self, inputs, weight, b_is_kn, out, roles=3):
         comm = self.comm
         rows_in = inputs[0].shape[0]
-        if any(t.shape != inputs[0].shape for t in inputs):
+        grouped = self.layout is not None and len(inputs) > 1
+        if any(t.shape != inputs[0].shape for t in inputs) and not (
+                grouped and all(t.shape[0] == rows_in and t.is_contiguous() for t in inputs)):
             raise ValueError('All head-side inputs must have the same shape')
         if rows_in % comm.p:
             raise ValueError('Head-side rows must divide evenly over CP ranks')
         src_rows = rows_in // comm.p
+        if grouped:
+            if not b_is_kn:
+                raise ValueError('The grouped-query dgrad takes the weight as [K, N]')
+            comm.recv_gqa(self.recv, weight, out, self.peer_recv, self.peer_counters, self.counters, inputs, src_rows,
+                          self.layout, roles=roles)
+            return
         if self.precision != 'mxfp8':
             comm.gemm('recv', self.recv, weight, b_is_kn, out, [self.peer_recv, self.peer_counters],
                       self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
@@ -954,6 +1035,7 @@ class FusedGemmA2AWorkspace:
     cp_group: object = None
     gate: bool = False
     precision: str = "bf16"
+    num_kv_heads: int = None          # fewer than num_heads: grouped-query attention (an addition to the reference)
     comm: object = field(init=False, repr=False)
     _buffers: dict = field(init=False, repr=False)
 
@@ -976,12 +1058,20 @@ class FusedGemmA2AWorkspace:
         if self.num_heads % peers or per_rank_width % MMA_N or per_rank_width % MMA_N_OUT_PUSH:
             raise ValueError('Heads must split over CP with tile-aligned per-rank width')
         _one_tile_per_head(head_dim, MMA_N)
+        kv_heads = self.num_kv_heads or self.num_heads
+        if kv_heads != self.num_heads:
+            if kv_heads < 1 or self.num_heads % kv_heads or kv_heads % peers:
+                raise ValueError('Query heads must be a multiple of key/value heads, which must split over CP')
+            if quantized:
+                raise NotImplementedError('MXFP8 with grouped-query attention is not supported yet')
         comm = _Comm.get(group)
         # One buffer set for the QKV(/gate) side and one for the output side, shared by every
         # workspace handle and layer of the same geometry on this group.
         sets = {}
         for segments in (4 if self.gate else 3, 1):
             geometry = (capacity, self.hidden_size, head_dim, segments)
+            if segments > 1 and kv_heads != self.num_heads:
+                geometry += (kv_heads * head_dim,)
             if geometry not in comm.projection_buffers:
                 comm.projection_buffers[geometry] = _ProjectionBuffers(comm, *geometry)
             sets[segments] = comm.projection_buffers[geometry]
@@ -996,7 +1086,8 @@ class FusedGemmA2AWorkspace:
         if self.precision == 'mxfp8' and type(weight) not in (torch.Tensor, nn.Parameter):
             raise TypeError('MXFP8 currently takes BF16 master weights, not quantized Parameter subclasses')
         same_geometry = (weight.shape[1] == self.hidden_size and module.num_heads == self.num_heads
-                         and module.segments in self._buffers)
+                         and module.segments in self._buffers
+                         and getattr(module, 'num_kv_heads', None) in (None, self.num_kv_heads or self.num_heads))
         if not same_geometry:
             raise ValueError('Workspace hidden size, head count and QKV/QKVG mode must match the projection')
         if weight.device != device or torch.cuda.current_device() != device.index:
@@ -1073,12 +1164,18 @@ class FusedQKVProjection(_CallerOwnedProjection):
         self._adopt(hidden_size, num_heads, weight, bias, apply_bias, accumulate_bias_grad)
         self.bias_in_gemm = bias_in_gemm
         self.segments = 4 if gate else 3
+        self.num_kv_heads = num_kv_heads or num_heads
         self.n_q = num_heads * self.head_dim
-        self.n_kv = (num_kv_heads or num_heads) * self.head_dim
+        self.n_kv = self.num_kv_heads * self.head_dim
         if self.n_kv != self.n_q:
-            raise NotImplementedError('GQA is not supported yet; Q, K and V must have equal widths')
+            # Grouped-query attention (rejected by the reference's fused modules, fused_gemm_a2a.py:592-593;
+            # its unfused baseline supports it): weight rows grouped per key/value head,
+            # [q_g0 .. q_g(r-1); k_g; v_g; (gate_g0 .. gate_g(r-1))], Megatron's order of a fused QKV weight.
+            if self.num_kv_heads < 1 or num_heads % self.num_kv_heads:
+                raise ValueError('Query heads must be a multiple of key/value heads')
+            self.weight_layout = 'group_qkvg'
         _one_tile_per_head(self.head_dim, MMA_TILER_MN[1])
-        self._keep(weight, bias, self.segments * self.n_q, hidden_size)
+        self._keep(weight, bias, self.n_q * (2 if gate else 1) + 2 * self.n_kv, hidden_size)
 
     def forward(self, x, workspace):
         _check_workspace(workspace, self, x)

@@ -133,6 +133,27 @@ int fga_gemm_recv(const void* recv, int recv_rows, int k, const void* b, int b_i
                   int rank, int p, int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
                   uint64_t timeout_ns, void* stream);
 
+/* Grouped-query attention: q_per_kv query heads share one key/value head. The weight rows of the QKV
+ * projection (= output columns of the push, = receive-buffer columns of its dgrad) are grouped per
+ * key/value head, [q_g0 .. q_g(r-1); k_g; v_g; (gate_g0 .. gate_g(r-1))] with r = q_per_kv, each head
+ * 128 rows; rank d owns the kv_heads / p consecutive groups d*kv_heads/p ... With q_per_kv == 1 this is
+ * the per-head order of fga_gemm_push / fga_gemm_recv with 3 or 4 segments. The reference rejects
+ * these shapes in its fused modules (fused_gemm_a2a.py:592-593) and supports them only in its unfused
+ * baseline (benchmark/reference.py:151-163), which is what the results are checked against.
+ *   push: peer_heads holds 3 (4 with gate) tables: q, k, v(, gate). The q and gate buffers are
+ *         [p*head_rows, kv_heads/p * q_per_kv * 128], the k and v buffers [p*head_rows, kv_heads/p * 128].
+ *         a [m, k] * b^T with b [kv_heads*(q_per_kv*(1+gate)+2)*128, k]; bias indexed by weight row.
+ *   recv: srcs holds the head-side gradients in the same order and with those widths
+ *         ([p*src_rows, width]); recv is [recv_rows, K] with K = kv_heads*(q_per_kv*(1+gate)+2)*128 in
+ *         weight-row order; c [recv_rows, n] = recv * b with b [K, n]. */
+int fga_gemm_push_gqa(const void* a, int m, int k, int a_rows, const void* b, const void* bias, int kv_heads,
+                      int q_per_kv, int gate, const int64_t* const* peer_heads, int64_t head_rows, int rank,
+                      int p, int32_t* status, uint64_t timeout_ns, void* stream);
+int fga_gemm_recv_gqa(const void* recv, int recv_rows, const void* b, int n, void* c, const int64_t* peer_recv,
+                      const int64_t* peer_counters, int32_t* counters, const void* const* srcs, int kv_heads,
+                      int q_per_kv, int gate, int src_rows, int split, int rank, int p, int roles,
+                      int32_t* progress, int32_t* status, uint64_t timeout_ns, void* stream);
+
 /* local: c[m, n] (=|+=) a * b^T with a as [m, k] (a_is_km == 0) or [k, m] (a_is_km != 0, read
  * transposed) and b as [n, k] or [k, n]. out_f32 selects FP32 output; accumulate (FP32 only) adds
  * into c. Rows of the reduction axis beyond k read as zero. With a_is_km = b_is_kn = 1 this is

@@ -222,3 +222,101 @@ def reduce_bias_grad_ref(dy, out_dtype, previous=None):
     if previous is not None:
         total = total + previous.double()
     return total.to(out_dtype)
+
+
+# ---------------------------------------------------------------------- grouped-query attention
+def interleave_gqa_rows(segment_major, heads, kv_heads, head_dim, gate=False):
+    """Rows in segment-major order [Q (heads); K (kv_heads); V (kv_heads)(; G (heads))] -> grouped
+    order, one group per key/value head: [q_g0 .. q_g(r-1); k_g; v_g(; gate_g0 .. gate_g(r-1))]
+    with r = heads / kv_heads. For r = 1 this is interleave_qkv_rows. The reference's unfused
+    baseline keeps one weight per projection (benchmark/reference.py:151-163, with
+    num_kv_heads < num_heads); the grouped order is Megatron's layout of a fused QKV weight under
+    grouped-query attention."""
+    r = heads // kv_heads
+    if heads % kv_heads or segment_major.shape[0] != (heads * (2 if gate else 1) + 2 * kv_heads) * head_dim:
+        raise ValueError('rows are not Q, K, V (and gate) blocks of these head counts')
+    tail = tuple(segment_major.shape[1:])
+    q_rows, kv_rows = heads * head_dim, kv_heads * head_dim
+    q = segment_major[:q_rows].reshape((kv_heads, r, head_dim) + tail)
+    k = segment_major[q_rows:q_rows + kv_rows].reshape((kv_heads, 1, head_dim) + tail)
+    v = segment_major[q_rows + kv_rows:q_rows + 2 * kv_rows].reshape((kv_heads, 1, head_dim) + tail)
+    parts = [q, k, v]
+    if gate:
+        parts.append(segment_major[q_rows + 2 * kv_rows:].reshape((kv_heads, r, head_dim) + tail))
+    return torch.cat(parts, dim=1).reshape((-1,) + tail)
+
+
+def deinterleave_gqa_rows(grouped, heads, kv_heads, head_dim, gate=False):
+    """Inverse of interleave_gqa_rows."""
+    r = heads // kv_heads
+    per_group = r * (2 if gate else 1) + 2
+    tail = tuple(grouped.shape[1:])
+    g = grouped.reshape((kv_heads, per_group, head_dim) + tail)
+    parts = [g[:, :r], g[:, r:r + 1], g[:, r + 1:r + 2]] + ([g[:, r + 2:]] if gate else [])
+    return torch.cat([part.reshape((-1,) + tail) for part in parts], dim=0)
+
+
+class GroupedQueryOracle(UlyssesOracle):
+    """UlyssesOracle with fewer key/value heads than query heads. weight_qkv / bias_qkv are in the
+    grouped row order of interleave_gqa_rows; outputs are q [P*M, N/P, D], k and v
+    [P*M, Nkv/P, D] (and gate like q). The output projection is unchanged."""
+
+    def __init__(self, p, hidden, heads, kv_heads, gate=False, **kwargs):
+        if heads % kv_heads or kv_heads % p:
+            raise ValueError('query heads must be a multiple of key/value heads, which must split over P')
+        super().__init__(p, hidden, heads, 4 if gate else 3, **kwargs)
+        self.kv, self.r, self.gate = kv_heads, heads // kv_heads, gate
+        self.per_group = self.r * (2 if gate else 1) + 2
+        # units of each kind inside a group: (first, count)
+        self.kinds = [(0, self.r), (self.r, 1), (self.r + 1, 1)] + ([(self.r + 2, self.r)] if gate else [])
+
+    def _by_kind(self, y):
+        """[rows, Nkv*per_group*D] in weight-row order -> per kind [rows, heads of that kind, D]."""
+        rows = y.shape[0]
+        g = y.reshape(rows, self.kv, self.per_group, self.d)
+        return [g[:, :, first:first + count].reshape(rows, self.kv * count, self.d) for first, count in self.kinds]
+
+    def qkv_forward(self, xs):
+        gpr = self.kv // self.p
+        ys = [self._by_kind(self.qkv_sequence_side(x)) for x in xs]
+        bias = None
+        if self.bq is not None and self.apply_bias and not self.bias_in_gemm:
+            bias = self._by_kind(self.bq.reshape(1, -1))
+        outs = []
+        for dest in range(self.p):
+            per_kind = []
+            for kind, (_, count) in enumerate(self.kinds):
+                heads_of_dest = slice(dest * gpr * count, (dest + 1) * gpr * count)
+                t = torch.cat([y[kind][:, heads_of_dest] for y in ys], dim=0).contiguous()
+                if bias is not None:
+                    t = (t.to(self.acc) + bias[kind][:, heads_of_dest].to(self.acc)).to(self.dtype)
+                per_kind.append(t)
+            outs.append(tuple(per_kind))
+        return outs
+
+    def qkv_heads_buffers(self, xs, capacity):
+        gpr = self.kv // self.p
+        bufs = [[torch.zeros(self.p * capacity, gpr * count * self.d, dtype=self.dtype) for _, count in self.kinds]
+                for _ in range(self.p)]
+        for r, x in enumerate(xs):
+            xp = torch.zeros(capacity, self.h, dtype=x.dtype)
+            xp[:x.shape[0]] = x
+            y = self._by_kind(self.qkv_sequence_side(xp))
+            for dest in range(self.p):
+                for kind, (_, count) in enumerate(self.kinds):
+                    bufs[dest][kind][r * capacity:(r + 1) * capacity] = \
+                        y[kind][:, dest * gpr * count:(dest + 1) * gpr * count].reshape(capacity, -1)
+        return bufs
+
+    def qkv_recv_buffer(self, grads, rank, capacity=None):
+        """dY of one rank in weight-row column order: grads[dest][kind] is [P*M, heads of that kind
+        per rank, D]; group g of destination dest is global group dest*gpr + g."""
+        gpr = self.kv // self.p
+        m = grads[0][0].shape[0] // self.p
+        rows = m if capacity is None else capacity
+        out = torch.zeros(rows, self.kv, self.per_group, self.d, dtype=grads[0][0].dtype)
+        for dest in range(self.p):
+            for kind, (first, count) in enumerate(self.kinds):
+                mine = grads[dest][kind][rank * m:(rank + 1) * m].reshape(m, gpr, count, self.d)
+                out[:m, dest * gpr:(dest + 1) * gpr, first:first + count] = mine
+        return out.reshape(rows, self.kv * self.per_group * self.d)

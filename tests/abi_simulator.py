@@ -226,6 +226,66 @@ class SimulatedLibrary:
             matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ weight.float().t()).to(BF16)
         return 0
 
+    # ---- grouped-query attention (contract: the grouped-query section of include/fga.h)
+    @staticmethod
+    def _kinds(q_per_kv, gate):
+        """(first unit, units) of q, k, v(, gate) inside one key/value group."""
+        return [(0, q_per_kv), (q_per_kv, 1), (q_per_kv + 1, 1)] + ([(q_per_kv + 2, q_per_kv)] if gate else [])
+
+    def fga_gemm_push_gqa(self, a, m, k, a_rows, b, bias, kv_heads, q_per_kv, gate, tables, head_rows, rank, p,
+                          status, timeout, stream):
+        self.launches += 1
+        kinds = self._kinds(q_per_kv, gate)
+        per_group, groups = kinds[-1][0] + kinds[-1][1], kv_heads // p
+        n = kv_heads * per_group * 128
+        padded = torch.zeros(a_rows, k, dtype=BF16)
+        padded[:m] = matrix(a, m, k)
+        product = padded.float() @ matrix(b, n, k).float().t()
+        if bias:
+            product = product + matrix(bias, 1, n).float()
+        product = product.to(BF16)
+        for unit in range(kv_heads * per_group):
+            group, position = divmod(unit, per_group)
+            kind = max(index for index, (first, _) in enumerate(kinds) if position >= first)
+            first, units = kinds[kind]
+            dest, local = divmod(group, groups)
+            column = (local * units + position - first) * 128
+            target = matrix(table(tables[kind], p)[dest], p * head_rows, groups * units * 128)
+            target[rank * head_rows:rank * head_rows + a_rows, column:column + 128] = product[:, unit * 128:(unit + 1) * 128]
+        return 0
+
+    def fga_gemm_recv_gqa(self, recv, recv_rows, b, n, c, peer_recv, peer_counters, counters, srcs, kv_heads, q_per_kv,
+                          gate, src_rows, split, rank, p, roles, progress, status, timeout, stream):
+        self.launches += 1
+        kinds = self._kinds(q_per_kv, gate)
+        per_group, groups = kinds[-1][0] + kinds[-1][1], kv_heads // p
+        k = kv_heads * per_group * 128
+        for turn in range(p if roles & 2 else 0):
+            if turn != rank:
+                dist.barrier()
+                continue
+            for dest in range(p):
+                target = matrix(table(peer_recv, p)[dest], recv_rows, k)
+                arrivals = torch.frombuffer(_bytes_at(table(peer_counters, p)[dest], 4 * (recv_rows // 128)),
+                                            dtype=torch.int32)
+                for kind, (first, units) in enumerate(kinds):
+                    width = groups * units * 128
+                    source = matrix(srcs[kind], p * src_rows, width)[dest * src_rows:(dest + 1) * src_rows]
+                    for unit in range(groups * units):
+                        local, within = divmod(unit, units)
+                        column = ((rank * groups + local) * per_group + first + within) * 128
+                        target[:src_rows, column:column + 128] = source[:, unit * 128:(unit + 1) * 128]
+                        target[src_rows:, column:column + 128] = 0
+                    arrivals += split
+            dist.barrier()
+        if not roles & 2:
+            dist.barrier()
+        if roles & 1:
+            if not self._arrived(counters, recv_rows, p * len(kinds) * split, roles):
+                return -2
+            matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ matrix(b, k, n).float()).to(BF16)
+        return 0
+
     def fga_gemm_recv_mx(self, recv, mx_recv, mx_scale, recv_rows, k, bq, sfb, b_rows_padded, b_kp, n, c,
                          peer_recv, peer_counters, counters, srcs, num_in, src_rows, split, rank, p, roles,
                          epoch, progress, status, timeout, stream):

@@ -15,8 +15,13 @@ UlyssesQKVProjection and UlyssesOutputProjection forward + backward and writes
                                       regenerated from the seed, so only strided samples and
                                       float64 checksums of every output are stored
 
+  tests/golden/ulysses_gqa_p2.npz     grouped-query attention (P=2, M=5, H=64, 8 query heads and
+                                      2 key/value heads of 8, QKVG with bias): the reference's
+                                      unfused modules with num_kv_heads < num_heads
+  tests/golden/ulysses_gqa_r2_p2.npz  the same with 4 key/value heads, QKV without bias
+
 The stored weights are segment-major [Q; K; V(; G)] exactly as the reference modules hold them; the
-tests interleave them per head before handing them to the oracle.
+tests interleave them per head (or per key/value group) before handing them to the oracle.
 """
 import argparse
 import os
@@ -61,9 +66,26 @@ def small_inputs(rank, p, m, hidden, heads, gate, bias, seed):
     return w, b, wo, bo, x, grads, o, dy
 
 
-def run_reference(ref, hidden, heads, gate, w, b, wo, bo, x, grads, o, dy):
+def gqa_inputs(rank, p, m, hidden, heads, kv_heads, gate, bias, seed):
+    """Like small_inputs with fewer key/value heads: K and V weights are [kv_heads*d, hidden]."""
+    d = hidden // heads
+    widths = [hidden, kv_heads * d, kv_heads * d] + ([hidden] if gate else [])
+    g = torch.Generator().manual_seed(seed)
+    w = [torch.randn(width, hidden, generator=g) / hidden ** 0.5 for width in widths]
+    b = [torch.randn(width, generator=g) for width in widths] if bias else None
+    wo = torch.randn(hidden, hidden, generator=g) / hidden ** 0.5
+    bo = torch.randn(hidden, generator=g) if bias else None
+    g = torch.Generator().manual_seed(seed + 1 + rank)
+    x = torch.randn(m, hidden, generator=g)
+    grads = [torch.randn(p * m, width // d // p, d, generator=g) for width in widths]
+    o = torch.randn(p * m, heads // p, d, generator=g)
+    dy = torch.randn(m, hidden, generator=g)
+    return w, b, wo, bo, x, grads, o, dy
+
+
+def run_reference(ref, hidden, heads, gate, w, b, wo, bo, x, grads, o, dy, kv_heads=None):
     """One forward + backward through the reference modules; returns a dict of float32 arrays."""
-    qkv = ref.UlyssesQKVProjection(hidden, heads, bias=b is not None, gate=gate, dtype=x.dtype)
+    qkv = ref.UlyssesQKVProjection(hidden, heads, kv_heads, bias=b is not None, gate=gate, dtype=x.dtype)
     out = ref.UlyssesOutputProjection(hidden, heads, bias=bo is not None, dtype=x.dtype)
     with torch.no_grad():
         for proj, weight in zip(qkv.projections, w):
@@ -108,6 +130,15 @@ def worker(rank, world, reference_root, port, queue):
         if rank == 0:
             res.update(w=torch.cat(w).numpy(), b=torch.cat(b).numpy(), wo=wo.numpy(), bo=bo.numpy())
         results['small_p2'] = res
+        for name, kv_heads, gate, bias, seed in (('gqa_p2', 2, True, True, 300), ('gqa_r2_p2', 4, False, False, 400)):
+            w, b, wo, bo, x, grads, o, dy = gqa_inputs(rank, 2, 5, 64, 8, kv_heads, gate, bias, seed)
+            res = run_reference(ref, 64, 8, gate, w, b, wo, bo, x, grads, o, dy, kv_heads=kv_heads)
+            res.update(x=x.numpy(), o=o.numpy(), dy=dy.numpy(), **{f'g{i}': t.numpy() for i, t in enumerate(grads)})
+            if rank == 0:
+                res.update(w=torch.cat(w).numpy(), wo=wo.numpy())
+                if bias:
+                    res.update(b=torch.cat(b).numpy(), bo=bo.numpy())
+            results[name] = res
         w, wo, x, grads, o, dy = c1_inputs(rank, 2, 512, 1024, 8)
         res = run_reference(ref, 1024, 8, False, w, None, wo, None, x, grads, o, dy)
         results['c1_p2'] = {k + '_sample': sample(v) for k, v in res.items()} | {

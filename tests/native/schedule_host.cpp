@@ -28,7 +28,35 @@ void sched_push_route(int col, int segments, int heads_per_rank, int* out) {
 
 long long sched_push_element(int col, int segments, int heads_per_rank, int rank, long long head_rows, int row,
                              long long head_pitch) {
-  return push_element(push_route(col, segments, heads_per_rank), rank, head_rows, row, head_pitch);
+  const PushRoute r = push_route(col, segments, heads_per_rank);
+  return r.pitch == head_pitch ? push_element(r, rank, head_rows, row) : -1;
+}
+
+// Grouped layouts (more query heads than key/value heads). out: segment, dest, column, pitch
+void sched_push_route_grouped(int col, int q_units, int kv_units, int gate_units, int groups_per_rank, int* out) {
+  const HeadLayout l{q_units, kv_units, gate_units, groups_per_rank};
+  const PushRoute r = push_route(col, l);
+  out[0] = r.segment;
+  out[1] = r.dest;
+  out[2] = r.column;
+  out[3] = r.pitch;
+}
+
+long long sched_push_element_grouped(int col, int q_units, int kv_units, int gate_units, int groups_per_rank, int rank,
+                                     long long head_rows, int row) {
+  const HeadLayout l{q_units, kv_units, gate_units, groups_per_rank};
+  return push_element(push_route(col, l), rank, head_rows, row);
+}
+
+long long sched_recv_column_grouped(int rank, int q_units, int kv_units, int gate_units, int groups_per_rank, int kind,
+                                    int unit) {
+  const HeadLayout l{q_units, kv_units, gate_units, groups_per_rank};
+  return recv_column(rank, l, kind, unit);
+}
+
+int sched_kind_pitch_units(int q_units, int kv_units, int gate_units, int groups_per_rank, int kind) {
+  const HeadLayout l{q_units, kv_units, gate_units, groups_per_rank};
+  return kind_pitch_units(l, kind);
 }
 
 long long sched_push_jobs_total(int m_tiles, int num_in, int p, int split) {

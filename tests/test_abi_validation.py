@@ -46,6 +46,16 @@ CASES = [
      'bias must be 16-byte aligned'),
     (recv_mx(c=P + 4), 'output must be 16-byte aligned'),
     (recv_mx(roles=0), 'roles'),
+    (('fga_gemm_push_gqa', (P, 300, 512, 512, P, None, 6, 4, 0, TABLES, 512, 0, 4, P, NS, None)), 'split evenly over CP'),
+    (('fga_gemm_push_gqa', (P, 300, 512, 512, P, None, 8, 0, 0, TABLES, 512, 0, 4, P, NS, None)), 'split evenly over CP'),
+    (('fga_gemm_push_gqa', (P, 300, 512, 300, P, None, 8, 4, 0, TABLES, 512, 0, 4, P, NS, None)), 'tile multiple'),
+    (('fga_gemm_push_gqa', (P, 300, 512, 512, P, P + 6, 8, 4, 1, TABLES, 512, 0, 4, P, NS, None)), 'bias must be 16-byte'),
+    (('fga_gemm_recv_gqa', (P, 512, P, 512, P, P, P, P, TABLES, 6, 2, 0, 300, 2, 0, 4, 3, None, P, NS, None)),
+     'split evenly over CP'),
+    (('fga_gemm_recv_gqa', (P, 512, P, 512, P, P, P, P, TABLES, 8, 2, 0, 600, 2, 0, 4, 3, None, P, NS, None)),
+     'Receive source rows'),
+    (('fga_gemm_recv_gqa', (P, 512, P, 512, P + 8, P, P, P, TABLES, 8, 2, 1, 300, 2, 0, 4, 3, None, P, NS, None)),
+     'output must be 16-byte aligned'),
     (recv(num_in=2), 'three/four'),
     (recv(recv_rows=300), 'multiple of 256'),
     (recv(src_rows=0), 'Receive source rows'),

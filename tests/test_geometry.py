@@ -173,8 +173,11 @@ def test_modules_validate_on_the_host_and_only_the_workspace_needs_a_group():
                                       apply_bias=False), ValueError, 'bias_in_gemm'),
     (lambda: fused.FusedQKVProjection(256, 2, weight=torch.empty(768, 256)), ValueError, 'weight must be'),
     (lambda: fused.FusedQKVProjection(256, 2, weight=torch.empty(1024, 256, dtype=BF16)), ValueError, 'weight must be'),
-    (lambda: fused.FusedQKVProjection(256, 2, 1, weight=torch.empty(768, 256, dtype=BF16)),
-     NotImplementedError, 'GQA'),
+    # grouped-query attention is accepted here (the reference's fused modules reject it): 2 query heads on
+    # 1 key/value head need 2 + 2 head blocks of weight rows, and the head counts must nest
+    (lambda: fused.FusedQKVProjection(256, 2, 1, weight=torch.empty(768, 256, dtype=BF16)), ValueError, 'weight must be'),
+    (lambda: fused.FusedQKVProjection(384, 3, 2, weight=torch.empty(896, 384, dtype=BF16)), ValueError,
+     'multiple of key/value heads'),
     (lambda: fused.FusedQKVProjection(256, 4, weight=torch.empty(768, 256, dtype=BF16)), ValueError,
      'one N tile per head'),
     (lambda: fused.FusedQKVProjection(250, 4, weight=torch.empty(750, 250, dtype=BF16)), ValueError, 'divisible'),
@@ -201,3 +204,14 @@ def test_wgrad_backend_variable_is_validated_like_the_reference():
             assert run.returncode == 0 and run.stdout.strip() == value, run.stderr[-500:]
         else:
             assert run.returncode != 0 and 'FUSED_WGRAD_BACKEND must be torch or fused_accum' in run.stderr
+
+
+def test_grouped_query_projection_takes_grouped_weight_rows():
+    module = fused.FusedQKVProjection(512, 4, 2, weight=torch.empty((4 + 2 * 2) * 128, 512, dtype=BF16))
+    assert (module.num_kv_heads, module.n_q, module.n_kv, module.segments) == (2, 512, 256, 3)
+    assert module.weight_layout == 'group_qkvg' and fused.FusedQKVProjection.weight_layout == 'head_qkvg'
+    gated = fused.FusedQKVProjection(512, 4, 1, gate=True, weight=torch.empty((4 * 2 + 2) * 128, 512, dtype=BF16),
+                                     bias=torch.empty((4 * 2 + 2) * 128, dtype=BF16))
+    assert gated.segments == 4 and gated.weight.shape[0] == 1280
+    same = fused.FusedQKVProjection(512, 4, 4, weight=torch.empty(3 * 512, 512, dtype=BF16))
+    assert same.weight_layout == 'head_qkvg' and same.num_kv_heads == 4

@@ -461,3 +461,104 @@ def test_workspaces_on_cp_subgroups_before_posted_pipeline_receives():
                 proc.terminate()
     for rank, problems in results:
         assert problems == [], f'rank {rank}: {problems}'
+
+
+def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, bias_in_gemm):
+    """The public modules with fewer key/value heads than query heads, on simulated ranks, against the
+    grouped-query oracle (itself pinned by the reference's unfused modules with num_kv_heads <
+    num_heads): outputs of different widths per kind, transport buffers bit for bit, dX, parameter
+    gradients in the grouped row order, and the output projection of the same workspace."""
+    for path in (HERE, os.path.dirname(HERE), os.path.join(os.path.dirname(HERE), 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    from oracle.ulysses_oracle import GroupedQueryOracle
+    p, d = world, 128
+    hidden = heads * d
+    r = heads // kv_heads
+    rows = (heads * (2 if gate else 1) + 2 * kv_heads) * d
+    kinds = 4 if gate else 3
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    problems = []
+    completed = False
+    try:
+        g = torch.Generator().manual_seed(77)
+        wq = (torch.randn(rows, hidden, generator=g) / 32).to(BF)
+        wo = (torch.randn(hidden, hidden, generator=g) / 32).to(BF)
+        bq = torch.randn(rows, generator=g).mul(0.5).to(BF) if bias else None
+        wq_p, wo_p = wq.clone().requires_grad_(), wo.clone().requires_grad_()
+        bq_p = bq.clone().requires_grad_() if bias else None
+        ws = fused.FusedGemmA2AWorkspace(hidden, heads, 300, gate=gate, num_kv_heads=kv_heads)
+        qkv = fused.FusedQKVProjection(hidden, heads, kv_heads, weight=wq_p, bias=bq_p, gate=gate,
+                                       bias_in_gemm=bias_in_gemm)
+        proj = fused.FusedOutputProjection(hidden, heads, weight=wo_p)
+        oracle = GroupedQueryOracle(p, hidden, heads, kv_heads, gate, weight_qkv=wq, bias_qkv=bq, weight_out=wo,
+                                    bias_in_gemm=bias_in_gemm)
+        widths = [heads // p if kind in (0, 3) else kv_heads // p for kind in range(kinds)]
+        for tokens in (129, 300):
+            g = torch.Generator().manual_seed(1000 * tokens + rank)
+            x = torch.randn(tokens, hidden, generator=g).to(BF).requires_grad_()
+            grads = [torch.randn(p * tokens, width, d, generator=g).to(BF) for width in widths]
+            o = torch.randn(p * tokens, heads // p, d, generator=g).to(BF).requires_grad_()
+            dy = torch.randn(tokens, hidden, generator=g).to(BF)
+            outs = qkv(x, ws)
+            view = ws._view(tokens, kinds)
+            xs = everyone(x.detach())
+            for kind, want in enumerate(oracle.qkv_heads_buffers(xs, view.capacity)[rank]):
+                landed(view.heads[kind], want, tokens, view.capacity, f'head buffer {kind} tokens={tokens}')
+            for name, got, want in zip('qkvg', outs, oracle.qkv_forward(xs)[rank]):
+                assert got.shape == want.shape, f'{name}: {tuple(got.shape)} vs {tuple(want.shape)}'
+                close(got, want, f'{name} tokens={tokens}')
+                assert got.data_ptr() not in {t.data_ptr() for t in view.heads}
+            got = torch.autograd.grad(outs, [x, wq_p] + ([bq_p] if bias else []), grads)
+            all_grads = everyone(tuple(grads))
+            same(view.recv, oracle.qkv_recv_buffer(all_grads, rank, view.capacity), f'dY transport tokens={tokens}')
+            assert view.counters.tolist() == [p * kinds * fused.push_split(kinds * hidden, p, kinds)] * (view.capacity // 128)
+            rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
+            close(got[0], rdx, 'dx')
+            close(got[1], rdw, 'dW_qkv (grouped row order)')
+            if bias:
+                close(got[2], rdb, 'dbias_qkv')
+            y = proj(o, ws)
+            close(y, oracle.out_forward(everyone(o.detach()))[rank], 'y')
+            do, dwo = torch.autograd.grad(y, [o, wo_p], dy)
+            rdos, rparams = oracle.out_backward(everyone(o.detach()), everyone(dy))
+            close(do, rdos[rank], 'dO')
+            close(dwo, rparams[rank][0], 'dW_o')
+        completed = True
+    except AssertionError as error:
+        problems.append(str(error))
+    finally:
+        undo(meet=completed)
+    queue.put((rank, problems))
+    if completed:
+        dist.destroy_process_group()
+    else:
+        os._exit(1)
+
+
+@pytest.mark.parametrize('world,heads,kv_heads,gate,bias,bias_in_gemm', [
+    (1, 4, 2, False, False, False), (2, 8, 2, True, True, False), (2, 4, 2, False, True, True), (2, 6, 2, False, False, False)])
+def test_grouped_query_modules_on_simulated_ranks(world, heads, kv_heads, gate, bias, bias_in_gemm):
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=grouped_query_worker,
+                         args=(r, world, 29640 + heads + world, queue, heads, kv_heads, gate, bias, bias_in_gemm))
+             for r in range(world)]
+    for proc in procs:
+        proc.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(queue.get(timeout=600))
+    finally:
+        for proc in procs:
+            proc.join(timeout=30)
+            if proc.is_alive():
+                proc.terminate()
+    for rank, problems in sorted(results):
+        assert problems == [], f'rank {rank}: {problems}'

@@ -119,3 +119,55 @@ def test_padded_buffers_match_unpadded_flow():
     for r in range(p):
         padded = oracle.qkv_recv_buffer(grads, r, capacity)
         assert torch.equal(padded[:m], oracle.qkv_recv_buffer(grads, r)) and not padded[m:].any()
+
+
+@pytest.mark.parametrize('name,kv_heads,gate,bias', [('gqa_p2', 2, True, True), ('gqa_r2_p2', 4, False, False)])
+def test_grouped_query_oracle_reproduces_reference_modules(name, kv_heads, gate, bias):
+    """The reference's unfused modules with num_kv_heads < num_heads (benchmark/reference.py:151-163):
+    8 query heads over 2 (or 4) key/value heads on two ranks. The oracle takes the weights in the
+    grouped row order [q_g0..; k_g; v_g; (gate_g0..)]; parameter gradients come back in that order."""
+    from oracle.ulysses_oracle import GroupedQueryOracle, deinterleave_gqa_rows, interleave_gqa_rows
+    z = np.load(os.path.join(GOLDEN, f'ulysses_{name}.npz'))
+    p, hidden, heads = 2, 64, 8
+    d = hidden // heads
+    kinds = 4 if gate else 3
+    wq = interleave_gqa_rows(torch.from_numpy(z['w']), heads, kv_heads, d, gate)
+    bq = interleave_gqa_rows(torch.from_numpy(z['b']), heads, kv_heads, d, gate) if bias else None
+    wo = torch.from_numpy(z['wo'])
+    bo = torch.from_numpy(z['bo']) if bias else None
+    oracle = GroupedQueryOracle(p, hidden, heads, kv_heads, gate, weight_qkv=wq, bias_qkv=bq, weight_out=wo,
+                                bias_out=bo, dtype=torch.float32, acc_dtype=torch.float64)
+    xs, os_, dys = tensors(z, p, 'x'), tensors(z, p, 'o'), tensors(z, p, 'dy')
+    grads = [tuple(torch.from_numpy(z[f'r{r}_g{i}']) for i in range(kinds)) for r in range(p)]
+    outs = oracle.qkv_forward(xs)
+    back = oracle.qkv_backward(xs, grads)
+    ys = oracle.out_forward(os_)
+    dos, out_params = oracle.out_backward(os_, dys)
+    for r in range(p):
+        assert [tuple(t.shape) for t in outs[r]] == [tuple(z[f'r{r}_out{i}'].shape) for i in range(kinds)]
+        assert outs[r][1].shape[1] == kv_heads // p and outs[r][0].shape[1] == heads // p
+        for i in range(kinds):
+            near(outs[r][i], z[f'r{r}_out{i}'], f'rank {r} output {i}')
+        dx, dw, db = back[r]
+        near(dx, z[f'r{r}_dx'], f'rank {r} dx')
+        near(deinterleave_gqa_rows(dw, heads, kv_heads, d, gate), z[f'r{r}_dw'], f'rank {r} dW_qkv')
+        near(ys[r], z[f'r{r}_y'], f'rank {r} y')
+        near(dos[r], z[f'r{r}_do'], f'rank {r} dO')
+        near(out_params[r][0], z[f'r{r}_dwo'], f'rank {r} dW_o')
+        if bias:
+            near(deinterleave_gqa_rows(db, heads, kv_heads, d, gate), z[f'r{r}_db'], f'rank {r} dbias_qkv')
+    # the padded transport buffers carry exactly the unpadded results in their logical rows
+    capacity = 16
+    bufs = oracle.qkv_heads_buffers(xs, capacity)
+    oracle_no_late_bias = GroupedQueryOracle(p, hidden, heads, kv_heads, gate, weight_qkv=wq, weight_out=wo,
+                                             dtype=torch.float32, acc_dtype=torch.float64)
+    plain = oracle_no_late_bias.qkv_forward(xs)
+    m = xs[0].shape[0]
+    for dest in range(p):
+        for kind in range(kinds):
+            blocks = bufs[dest][kind].view(p, capacity, -1)
+            assert torch.equal(blocks[:, :m].reshape(plain[dest][kind].shape), plain[dest][kind])
+            assert not blocks[:, m:].any()
+    for r in range(p):
+        padded = oracle.qkv_recv_buffer(grads, r, capacity)
+        assert torch.equal(padded[:m], oracle.qkv_recv_buffer(grads, r)) and not padded[m:].any()

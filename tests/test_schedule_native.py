@@ -15,7 +15,7 @@ import pytest
 import torch
 
 from oracle import mxfp8_oracle
-from oracle.ulysses_oracle import UlyssesOracle
+from oracle.ulysses_oracle import GroupedQueryOracle, UlyssesOracle
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 I = ctypes.c_int
@@ -28,8 +28,10 @@ def sched(tmp_path_factory):
     subprocess.run(['g++', '-O1', '-std=c++17', '-shared', '-fPIC', '-Wall', '-Werror', '-x', 'c++',
                     os.path.join(HERE, 'native', 'schedule_host.cpp'), '-o', str(out)], check=True)
     lib = ctypes.CDLL(str(out))
-    for name in ('sched_push_element', 'sched_push_jobs_total', 'sched_first_phase_jobs', 'sched_recv_column'):
+    for name in ('sched_push_element', 'sched_push_jobs_total', 'sched_first_phase_jobs', 'sched_recv_column',
+                 'sched_push_element_grouped', 'sched_recv_column_grouped'):
         getattr(lib, name).restype = L
+    lib.sched_push_element_grouped.argtypes = [I, I, I, I, I, I, L, I]
     lib.sched_push_element.argtypes = [I, I, I, I, L, I, L]
     lib.sched_decode_push_job.argtypes = [L, I, I, I, I, ctypes.POINTER(I)]
     lib.sched_pick_k_splits.argtypes = [L, I, I, I]
@@ -242,6 +244,85 @@ def test_receive_columns_match_the_oracle_layout(sched, p, hidden, heads, num_in
                     column = sched.sched_recv_column(r, hpr, unit, num_in, t)
                     got[:, column:column + 128] = block[:, unit]
         assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------------------------ grouped-query layouts
+class _CodedGroupedOracle(GroupedQueryOracle):
+    """The grouped-query oracle with the QKV GEMM replaced by a table of codes (see _CodedOracle)."""
+
+    def __init__(self, codes, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.codes = codes
+
+    def qkv_sequence_side(self, x):
+        table = self.codes[int(x[0, 0])]
+        out = torch.zeros(x.shape[0], table.shape[1])
+        out[:table.shape[0]] = table
+        return out
+
+
+@pytest.mark.parametrize('p,heads,kv_heads,gate', [(1, 8, 2, False), (2, 8, 2, True), (2, 8, 4, False), (4, 32, 8, False),
+                                                   (8, 64, 8, True), (8, 32, 8, False), (2, 6, 6, True)])
+def test_grouped_push_routing_and_receive_columns_match_the_oracle(sched, p, heads, kv_heads, gate):
+    """More query heads than key/value heads: every output element of every source rank lands in the
+    head-side buffer (kind, destination, column, row pitch) where the grouped-query oracle has it, and
+    the pushers' receive columns rebuild the oracle's receive buffer. The oracle itself is pinned by the
+    reference's unfused modules run with num_kv_heads < num_heads."""
+    d, tokens, capacity = 128, 2, 256
+    hidden = heads * d
+    r, gpr = heads // kv_heads, kv_heads // p
+    layout = (r, 1, r if gate else 0, gpr)
+    kinds = 4 if gate else 3
+    n = kv_heads * (r * (2 if gate else 1) + 2) * d
+    codes = [torch.arange(1, tokens * n + 1, dtype=torch.float32).reshape(tokens, n) + 1e7 * rank for rank in range(p)]
+    oracle = _CodedGroupedOracle(codes, p, hidden, heads, kv_heads, gate, dtype=torch.float32)
+    xs = [torch.full((tokens, hidden), float(rank)) for rank in range(p)]
+    expected = oracle.qkv_heads_buffers(xs, capacity)
+    got = [[torch.zeros_like(expected[dest][kind]) for kind in range(kinds)] for dest in range(p)]
+    out = (I * 4)()
+    for rank in range(p):
+        for col in range(0, n, 128):                      # one unit at a time: 128 columns move together
+            sched.sched_push_route_grouped(col, *layout, out)
+            kind, dest, column, pitch = tuple(out)
+            assert 0 <= kind < kinds and 0 <= dest < p and pitch == expected[dest][kind].shape[1]
+            assert pitch == 128 * sched.sched_kind_pitch_units(*layout, kind) and 0 <= column <= pitch - 128
+            for row in range(tokens):
+                element = sched.sched_push_element_grouped(col, *layout, rank, capacity, row)
+                assert element == (rank * capacity + row) * pitch + column
+                got[dest][kind].view(-1)[element:element + 128] = codes[rank][row, col:col + 128]
+    for dest in range(p):
+        for kind in range(kinds):
+            assert torch.equal(got[dest][kind], expected[dest][kind]), (dest, kind)
+    # receive side: rank `rank` pushes unit u of its kind-`kind` input for destination dest
+    widths = [gpr * (r if kind in (0, 3) else 1) for kind in range(kinds)]
+    sources = [tuple(torch.arange(p * tokens * widths[kind] * d, dtype=torch.float32).reshape(p * tokens, widths[kind], d)
+                     + 1e7 * rank + 1e6 * kind for kind in range(kinds)) for rank in range(p)]
+    for dest in range(p):
+        want = oracle.qkv_recv_buffer(sources, dest)
+        rebuilt = torch.full_like(want, -1.0)
+        for rank in range(p):
+            for kind in range(kinds):
+                block = sources[rank][kind][dest * tokens:(dest + 1) * tokens]
+                assert sched.sched_kind_pitch_units(*layout, kind) == widths[kind]
+                for unit in range(widths[kind]):
+                    column = sched.sched_recv_column_grouped(rank, *layout, kind, unit)
+                    rebuilt[:, column:column + d] = block[:, unit]
+        assert torch.equal(rebuilt, want)
+
+
+def test_uniform_layout_is_the_grouped_layout_with_one_query_head_per_group(sched):
+    out3, out4 = (I * 3)(), (I * 4)()
+    for segments, hpr in ((1, 4), (3, 4), (4, 3), (3, 5)):
+        layout = (1, 1 if segments > 1 else 0, 1 if segments == 4 else 0, hpr)
+        for col in range(0, 2 * segments * hpr * 128, 64):
+            sched.sched_push_route(col, segments, hpr, out3)
+            sched.sched_push_route_grouped(col, *layout, out4)
+            assert tuple(out3) == tuple(out4)[:3] and out4[3] == hpr * 128
+        for rank in range(2):
+            for t in range(segments):
+                for unit in range(hpr):
+                    assert sched.sched_recv_column(rank, hpr, unit, segments, t) == \
+                        sched.sched_recv_column_grouped(rank, *layout, t, unit)
 
 
 # ------------------------------------------------------------------------------------ MXFP8 rule
