@@ -119,6 +119,15 @@ static int pace_pushers(GemmParams& P, int32_t* progress, cudaStream_t stream) {
   return kSuccess;
 }
 
+// N tile of a block-scaled GEMM: 256 columns where the widths allow it, with a single accumulator
+// stage (the scale columns take the TMEM that a second 256-column stage would need, so a tile's
+// epilogue does not overlap the next tile's mainloop), else 128 columns with two stages.
+// FGA_MX_TILE_N=128 forces the narrow, double-buffered form everywhere, for measuring one against
+// the other; both forms are the same code path with different tile counts.
+static int mx_tile_n(bool wide_allowed) {
+  return wide_allowed && env_int("FGA_MX_TILE_N", 256) != 128 ? 256 : 128;
+}
+
 // Block-scaled instruction descriptor: E4M3 x E4M3, E8M0 scales, M = 256 across the pair, N = bn.
 // The scale-byte selectors (bits 4-5 and 29-30) are filled in per K block by the kernel.
 static uint32_t make_idesc_mx(int bn) {
@@ -440,7 +449,7 @@ int fga_gemm_local_mx(const void* aq, const void* sfa, int64_t a_rows_padded, co
   GemmParams P{};
   P.mode = kLocal;
   P.epi = out_f32 ? (accumulate ? kEpiF32Add : kEpiF32Store) : kEpiBf16;
-  P.bn = (n % 256 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.bn = mx_tile_n(n % 256 == 0 && b_rows_padded % 256 == 0);
   P.acc_stages = P.bn == 256 ? 1 : 2;
   P.m_tiles = (m + 255) / 256;
   P.n_tiles = n / P.bn;
@@ -482,7 +491,7 @@ int fga_gemm_push_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int
   for (int s = 0; s < segments; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_mx: null peer table %d", s);
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push_mx: the bias must be 16-byte aligned");
   GemmParams P{};
-  P.bn = ((n / 128) % 2 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.bn = mx_tile_n((n / 128) % 2 == 0 && b_rows_padded % 256 == 0);
   P.acc_stages = P.bn == 256 ? 1 : 2;
   P.m_tiles = a_rows / 256;
   P.k_tiles = kp / 128;
@@ -524,7 +533,7 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
                 "fga_gemm_recv_mx: source %d must be a 16-byte aligned device pointer", t);
   FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv_mx: output must be 16-byte aligned");
   GemmParams P{};
-  P.bn = (n % 256 == 0 && b_rows_padded % 256 == 0) ? 256 : 128;
+  P.bn = mx_tile_n(n % 256 == 0 && b_rows_padded % 256 == 0);
   P.acc_stages = P.bn == 256 ? 1 : 2;
   P.k_tiles = k / 128;
   P.idesc = make_idesc_mx(P.bn);

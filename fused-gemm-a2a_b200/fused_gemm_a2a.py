@@ -72,6 +72,14 @@ if SYMM_BACKEND not in ('auto', 'ipc', 'vmm'):
 # Seconds a rank waits for a peer while file descriptors are handed around (FGA_SYMM=vmm / auto).
 DESCRIPTOR_TIMEOUT_S = float(os.environ.get('FGA_DESCRIPTOR_TIMEOUT_S', 60))
 
+# FGA_MX_WEIGHT_CACHE=1 (off by default; MXFP8 only): keep the quantized copy of a weight, per
+# reduction axis, for as long as the weight tensor is unchanged (same storage, same autograd version
+# counter), instead of requantizing it from BF16 on every call as the reference does. The result is
+# bit-identical; it saves one pass over the weight per GEMM and holds two E4M3 copies (as many bytes
+# as the BF16 weight). Never used during graph capture: a captured step quantizes inside the graph,
+# because a replay must see the weights an optimizer step has written in between.
+MX_WEIGHT_CACHE = os.environ.get('FGA_MX_WEIGHT_CACHE', '0') == '1'
+
 # With FGA_CHECK_STATUS_EVERY=N every N-th forward of a group synchronizes and raises when a device
 # wait has expired since the last check (never during graph capture). Off by default (0): the status
 # word is then surfaced without synchronizing, see _Comm.post_status / poll_status.
@@ -939,6 +947,22 @@ class _ProjectionBuffers:
         self.mx_scale = torch.empty((rows * k // 32,), device=device, dtype=torch.uint8)
 
 
+_quantized_weights = {}
+
+
+def _quantized_weight(weight, transposed):
+    """mxfp8_quantize(weight.T if transposed else weight), through the opt-in cache (see MX_WEIGHT_CACHE)."""
+    view = weight.T if transposed else weight
+    if not MX_WEIGHT_CACHE or torch.cuda.is_current_stream_capturing():
+        return mxfp8_quantize(view)
+    slot = (weight.data_ptr(), tuple(weight.shape), transposed)
+    version = weight._version
+    cached = _quantized_weights.get(slot)
+    if cached is None or cached[0] != version:
+        cached = _quantized_weights[slot] = (version, mxfp8_quantize(view))
+    return cached[1]
+
+
 class _ProjectionWorkspace:
     """Views of the fixed allocation sized for one invocation's active capacity
     (reference fused_gemm_a2a.py:424-473)."""
@@ -972,7 +996,7 @@ class _ProjectionWorkspace:
         # MXFP8: both operands are requantized from BF16 on every call, each along this GEMM's
         # reduction axis (reference fused_gemm_a2a.py:439-448).
         aq, sa = mxfp8_quantize(a)
-        wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+        wq, sb = _quantized_weight(weight, b_is_kn)
         comm.gemm('push', aq, wq, False, self.heads[0], self.peer_heads, self.counters, 0, n_segment,
                   segments, a_rows=self.capacity, head_dim=self.head_dim, bias=bias, scales=(sa, sb))
 
@@ -1002,7 +1026,7 @@ class _ProjectionWorkspace:
             return
         # MXFP8: only BF16 crosses the links; quantizer warps inside the kernel convert each arrived
         # row block into the local E4M3 copy that the GEMM reads (reference fused_gemm_a2a.py:465-470).
-        wq, sb = mxfp8_quantize(weight.T if b_is_kn else weight)
+        wq, sb = _quantized_weight(weight, b_is_kn)
         comm.gemm('recv', self.mx_recv, wq, False, out, [self.peer_recv, self.peer_counters],
                   self.counters, len(inputs), 0, 1, srcs=[t.data_ptr() for t in inputs],
                   head_dim=self.head_dim, src_rows=src_rows, scales=(self.mx_scale, sb), roles=roles)

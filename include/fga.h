@@ -26,7 +26,8 @@
  *   - tuning variables are read from the environment by the launcher, on the host, at every call:
  *     FGA_STAGES, FGA_GROUP_M_PUSH, FGA_GROUP_M_RECV, FGA_GROUP_M_LOCAL (raster group sizes),
  *     FGA_PUSHER_WARPS, FGA_PUSH_LEAD, FGA_WGRAD_SPLITS (fga_gemm_local with FP32 output: shares of the
- *     reduction axis per tile, a number or "auto"). Unset means the defaults that were measured; none
+ *     reduction axis per tile, a number or "auto"), FGA_MX_TILE_N (128: block-scaled GEMMs use 128-column
+ *     tiles with two accumulator stages everywhere instead of 256-column tiles with one). Unset means the defaults that were measured; none
  *     of them changes results beyond FP32 summation order. A launch captured into a CUDA graph keeps
  *     the values it was captured with: changing a variable afterwards does not affect replays.
  */

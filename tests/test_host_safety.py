@@ -331,3 +331,51 @@ def test_sigterm_drains_first_and_then_ends_the_process_by_the_same_signal():
                             text=True, timeout=120)
     assert result.stdout.split() == ['drained']
     assert result.returncode == -signal.SIGTERM
+
+
+# ------------------------------------------------------------------------- MXFP8 weight cache
+def _weight_cache_worker(rank, world, port, queue):
+    _join(port, rank, world)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    counts = {}
+    try:
+        quantize, calls = fused.mxfp8_quantize, []
+
+        def counting(a, *, k_multiple=256):
+            calls.append(tuple(a.shape))
+            return quantize(a, k_multiple=k_multiple)
+
+        fused.mxfp8_quantize = counting
+        ws = fused.FusedGemmA2AWorkspace(512, 4, 300, precision='mxfp8')
+        weight = (torch.randn(1536, 512) / 32).to(torch.bfloat16).requires_grad_()
+        qkv = fused.FusedQKVProjection(512, 4, weight=weight)
+        x = torch.randn(129, 512).to(torch.bfloat16).requires_grad_()
+
+        def step():
+            del calls[:]
+            outs = qkv(x, ws)
+            torch.autograd.backward(list(outs), [torch.ones_like(t) for t in outs])
+            return sum(1 for shape in calls if 1536 in shape)      # quantizer passes over the weight
+
+        counts['off'] = [step(), step()]
+        fused.MX_WEIGHT_CACHE = True
+        fused._quantized_weights.clear()
+        counts['on'] = [step(), step(), step()]
+        with torch.no_grad():
+            weight.mul_(0.5)                                       # an optimizer step: the version counter moves
+        counts['after_update'] = [step(), step()]
+        queue.put((rank, counts))
+    finally:
+        fused.MX_WEIGHT_CACHE = False
+        fused._quantized_weights.clear()
+        undo()
+    dist.destroy_process_group()
+
+
+def test_quantized_weights_are_kept_only_while_the_weight_is_unchanged():
+    counts, = _run(_weight_cache_worker, 1, 29726)
+    assert counts['off'] == [2, 2]                  # forward (rows) and dgrad (columns): every call, as the reference does
+    assert counts['on'] == [2, 0, 0]
+    assert counts['after_update'] == [2, 0]
