@@ -88,28 +88,6 @@ def test_reduce_bias_grad_integer_sums_are_exact(native):
     assert torch.equal(out.cpu(), dy.float().sum(0))
 
 
-def test_reduce_bias_grad_rows_beyond_four_gibibytes(native):
-    """The last row of a [131073, 16384] BF16 matrix starts past 2^32 bytes and past 2^31 elements:
-    row offsets must be 64-bit (reference tests/bias_grad_driver.py:54-59). Exact: one row of ones,
-    all others zero. Also through the entry point with built-in scratch (513 x 16384 partial sums
-    do not fit its array, so it must refuse rather than wrap)."""
-    from fused_gemm_a2a_kernels import reduce_bias_grad
-    rows, width = 131073, 16384
-    dy = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
-    dy[-1] = 1
-    out = reduce_bias_grad(dy, torch.empty(width, dtype=torch.float32, device=DEV))
-    assert torch.equal(out, torch.ones_like(out))
-    dy[-1, 5] = 3
-    dy[70000, 5] = -8
-    out = reduce_bias_grad(dy, torch.zeros(width, dtype=torch.bfloat16, device=DEV))
-    expected = torch.ones(width)
-    expected[5] = -5
-    assert torch.equal(out.float().cpu(), expected)
-    rc = native.fga_bias_grad_static(dy.data_ptr(), rows, width, out.data_ptr(), 0, 0,
-                                     torch.cuda.current_stream().cuda_stream)
-    assert rc == -1 and b'scratch floats' in native.fga_last_error()
-
-
 def _bits(t):
     return t.view(torch.int16).cpu().numpy().view(np.uint16)
 

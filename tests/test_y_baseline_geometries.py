@@ -12,12 +12,22 @@ compared on a sample that the oracle can afford: whole 256-row blocks of the row
 (first, middle and the ragged last block) and whole 256 x 256 tiles of the weight gradients, which
 sum over every token. Tolerance as everywhere: max error <= 1e-2 of the reference's largest
 magnitude and relative Frobenius error <= 2e-3 for BF16 results; the MXFP8 quantized copy and its
-scales bit-exact against the standalone quantizer. The same heads-per-rank counts at CP = 8
-(4, 3 and 5) are covered by tests/test_emulated_ranks.py on one GPU and by the multi-GPU driver.
+scales bit-exact against the standalone quantizer. The same geometries at CP = 8 (4, 3 and 5 heads
+per rank) go through the one-GPU rank emulation of tests/test_emulated_ranks.py at the end of this
+file, and through the multi-GPU driver. Also here: the bias gradient of a matrix larger than 4 GiB.
+
+The file sorts after the tests of the small shapes on purpose: a run that stops at the first
+failure has then already been through every kernel on the sizes where a mismatch is cheap to read.
 """
+import os
+import sys
+
 import numpy as np
 import pytest
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import test_emulated_ranks as emulated  # noqa: E402
 
 from oracle import mxfp8_oracle as mx
 from oracle.ulysses_oracle import UlyssesOracle
@@ -188,3 +198,45 @@ def test_c5_mxfp8_hidden_5120_40_heads_outliers_zero_groups_main_grad(cp1):
             want = torch.from_numpy(mx.mx_matmul(bits(left[:, r0:r0 + 256].t()), bits(right[:, c0:c0 + 256].t()))).float()
             tile = added[r0:r0 + 256, c0:c0 + 256]
             assert (tile - want).abs().max() <= 1e-3 * want.abs().max(), f'dW_{name} tile {r0},{c0}'
+
+
+# ---- the same geometries at CP = 8 on one GPU: 4, 3 and 5 heads per rank -------------------------
+@pytest.mark.parametrize('p,hidden,heads,tokens,segments,bias_in_gemm', [
+    (8, 4096, 32, 129, 3, False), (8, 3072, 24, 77, 4, True), (8, 5120, 40, 129, 3, False)])
+def test_cp8_push_lands_in_the_right_peer_tiles(native, p, hidden, heads, tokens, segments, bias_in_gemm):
+    emulated.test_push_lands_in_the_right_peer_tiles(native, p, hidden, heads, tokens, segments, bias_in_gemm)
+
+
+@pytest.mark.parametrize('p,hidden,heads,tokens', [(8, 4096, 32, 129), (8, 3072, 24, 77), (8, 5120, 40, 31)])
+def test_cp8_output_dgrad_push_routes_columns_to_their_owner(native, p, hidden, heads, tokens):
+    emulated.test_output_dgrad_push_routes_columns_to_their_owner(native, p, hidden, heads, tokens)
+
+
+@pytest.mark.parametrize('p,hidden,heads,tokens,num_in', [
+    (8, 4096, 32, 129, 3), (8, 4096, 32, 129, 1), (8, 3072, 24, 77, 4), (8, 3072, 24, 77, 1),
+    (8, 5120, 40, 129, 3), (8, 5120, 40, 33, 1)])
+def test_cp8_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in):
+    emulated.test_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in)
+
+
+# ---- a matrix larger than 4 GiB -------------------------------------------------------------------
+def test_reduce_bias_grad_rows_beyond_four_gibibytes(native):
+    """The last row of a [131073, 16384] BF16 matrix starts past 2^32 bytes and past 2^31 elements:
+    row offsets must be 64-bit (reference tests/bias_grad_driver.py:54-59). Exact: one row of ones,
+    all others zero. Also through the entry point with built-in scratch (513 x 16384 partial sums
+    do not fit its array, so it must refuse rather than wrap)."""
+    from fused_gemm_a2a_kernels import reduce_bias_grad
+    rows, width = 131073, 16384
+    dy = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
+    dy[-1] = 1
+    out = reduce_bias_grad(dy, torch.empty(width, dtype=torch.float32, device=DEV))
+    assert torch.equal(out, torch.ones_like(out))
+    dy[-1, 5] = 3
+    dy[70000, 5] = -8
+    out = reduce_bias_grad(dy, torch.zeros(width, dtype=torch.bfloat16, device=DEV))
+    expected = torch.ones(width)
+    expected[5] = -5
+    assert torch.equal(out.float().cpu(), expected)
+    rc = native.fga_bias_grad_static(dy.data_ptr(), rows, width, out.data_ptr(), 0, 0,
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == -1 and b'scratch floats' in native.fga_last_error()
