@@ -530,7 +530,20 @@ class _Comm:
     def clear_status(self):
         """Zero the status word once a device error has been dealt with. The word is sticky: while
         it holds a code, barriers and fused GEMMs of this group return at entry without touching any
-        peer's memory, because the peer that never answered may have unmapped it."""
+        peer's memory, because the peer that never answered may have unmapped it.
+
+        Collective over the group when it has more than one rank: a barrier that returned at entry did
+        not advance this rank's epoch, so the ranks' epochs may differ by the number of barriers each
+        of them skipped, and a rank that is behind would sail through its next barriers on its peers'
+        older, higher flags. All ranks therefore drain their devices, meet on the host, zero their
+        barrier flags (every rank starts again from epoch 1) and meet again. Only meaningful while
+        every rank of the group is still alive; after a rank has died the group has to be rebuilt."""
+        if self.p > 1:
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+            self.flags.zero_()
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
         self.status.zero_()
         self._status_host.zero_()
         self._status_posted = False

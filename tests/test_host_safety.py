@@ -379,3 +379,26 @@ def test_quantized_weights_are_kept_only_while_the_weight_is_unchanged():
     assert counts['off'] == [2, 2]                  # forward (rows) and dgrad (columns): every call, as the reference does
     assert counts['on'] == [2, 0, 0]
     assert counts['after_update'] == [2, 0]
+
+
+def _resync_worker(rank, world, port, queue):
+    _join(port, rank, world)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    try:
+        ws = fused.FusedGemmA2AWorkspace(512, 4, 300)
+        comm = ws.comm
+        # as after a timed-out step: rank 1 skipped two barriers, so the epochs its peers wrote here are ahead
+        comm.flags.copy_(torch.tensor([7, 7] if rank == 0 else [5, 7], dtype=torch.int64))
+        comm.status.copy_(torch.tensor([1, 1, 6, 0], dtype=torch.int32))
+        comm.clear_status()
+        queue.put((rank, (comm.flags.tolist(), comm.status.tolist())))
+    finally:
+        undo()
+    dist.destroy_process_group()
+
+
+def test_clearing_the_status_word_puts_every_rank_back_on_the_same_barrier_epoch():
+    for flags, status in _run(_resync_worker, 2, 29727):
+        assert flags == [0, 0] and status == [0, 0, 0, 0]
