@@ -263,10 +263,14 @@ def _drain():
             pass
 
 
+_drain_registered = []
+
+
 def _drain_at_exit(comm):
     """Register a runtime for the interpreter-exit drain (installed once)."""
-    if not _live_comms:
+    if not _drain_registered:
         atexit.register(_drain)
+        _drain_registered.append(True)
     _live_comms.append(comm)
 
 
@@ -316,6 +320,8 @@ class _Comm:
 
     @classmethod
     def get(cls, group):
+        if group is None:
+            group = dist.group.WORLD      # one runtime per group, however the default group is spelled
         slot = (group, torch.cuda.current_device())
         existing = cls._instances.get(slot)
         if existing is not None:
