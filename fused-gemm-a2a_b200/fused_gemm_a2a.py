@@ -395,12 +395,20 @@ class _Comm:
     def _map_everywhere_ipc(self, nbytes):
         """cudaMalloc + one 64-byte CUDA IPC handle per rank."""
         lib, ct = _native.lib(), _native.ctypes
-        local = _native.c_void_p()
-        _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
+        local, handle, problem = _native.c_void_p(), ct.create_string_buffer(_HANDLE_BYTES), None
+        try:
+            _native.check(lib.fga_symm_alloc(nbytes, ct.byref(local)))
+            if self.p > 1:
+                _native.check(lib.fga_symm_export(local, handle))
+        except Exception as error:                 # noqa: BLE001  (the verdict must reach the all-reduce)
+            problem = error
+        if not self._everyone(problem is None):    # nobody enters the exchange unless everybody can
+            if local.value:
+                lib.fga_symm_free(local)
+            raise RuntimeError(f'Symmetric memory ({nbytes} bytes) could not be allocated on every rank '
+                               f'(rank {self.rank}: {problem!r})')
         if self.p == 1:
             return local.value, [local.value], nbytes
-        handle = ct.create_string_buffer(_HANDLE_BYTES)
-        _native.check(lib.fga_symm_export(local, handle))
 
         def open_peer(raw):
             remote = _native.c_void_p()
