@@ -53,9 +53,12 @@ LINK_GBS = 770.0
 # launches are too large to capture; traffic grows with the rows, so it is scaled by the FLOPs.
 DRAM_BYTES_PER_FLOP = dict(gemm=670.4e6 / 824.6e9, wgrad=1296.8e6 / 824.6e9)
 # Parity gate in front of the timed region: (max error / largest reference magnitude, relative
-# Frobenius error). BF16 as in the test-suite; MXFP8 is compared with the same FP32 products, so
-# its bound is the quantization error of E4M3 payloads with one scale per 32 elements.
-PARITY_TOLERANCE = dict(bf16=(1e-2, 2e-3), mxfp8=(1.5e-1, 5e-2))
+# Frobenius error). BF16 as in the test-suite. MXFP8 is compared with the same FP32 products of the
+# unquantized inputs, so its bound is the quantization noise itself: an E4M3 value (3 mantissa bits)
+# carries a relative rounding error of about 2.6 % RMS, a product of two about 3.7 %, and a sum of
+# independent terms keeps that ratio; 8 % leaves room for groups with outliers, whose small members
+# lose more, while a wrong head or row mapping shows up as an error of order 100 %.
+PARITY_TOLERANCE = dict(bf16=(1e-2, 2e-3), mxfp8=(2.5e-1, 8e-2))
 
 
 def parse_args(argv=None):
