@@ -118,3 +118,72 @@ def test_comparison_arm_computes_the_same_projections(world):
         assert p.exitcode == 0
     for rank, problems in results:
         assert problems == [], f'rank {rank}: {problems}'
+
+
+def fused_arm_worker(rank, world, port, queue, gate, bias):
+    """bench.FusedArm (the adapter between the public modules and the harness) over the simulated
+    library: its results, in the form the parity gate takes, must pass the gate at the BF16 bound."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    for path in (here, ROOT, os.path.join(ROOT, 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    import abi_simulator
+    import bench
+    import fused_gemm_a2a as fused
+    sim, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    problems = []
+    try:
+        hidden, heads, m, bf = 512, 4, 300, torch.bfloat16
+        segments, d = (4 if gate else 3), 128
+        g = torch.Generator().manual_seed(1234)
+        parameters = dict(w_seg=(torch.randn(segments * hidden, hidden, generator=g) / 64).to(bf),
+                          wo=(torch.randn(hidden, hidden, generator=g) / 64).to(bf),
+                          bq=(torch.randn(segments * hidden, generator=g) * 0.02).to(bf) if bias else None,
+                          bo=(torch.randn(hidden, generator=g) * 0.02).to(bf) if bias else None)
+        g = torch.Generator().manual_seed(1235 + rank)
+        data = dict(x=torch.randn(m, hidden, generator=g).to(bf),
+                    grads=[torch.randn(world * m, heads // world, d, generator=g).to(bf) for _ in range(segments)],
+                    o=torch.randn(world * m, heads // world, d, generator=g).to(bf),
+                    dy=torch.randn(m, hidden, generator=g).to(bf))
+        arm = bench.FusedArm(torch, fused, hidden, heads, m, data, parameters, gate=gate)
+        state = {}
+        for one_pass in arm.passes:
+            one_pass(state)
+        report, failures = bench.validate_step(
+            torch, dist, rank, world, hidden, heads,
+            dict(x=data['x'].detach(), grads=data['grads'], o=data['o'].detach(), dy=data['dy']), parameters,
+            arm.results(state), bench.parity_tolerance('bf16', bias))
+        problems += failures
+        if len(report) != segments + 1 + 2 * segments + 1 + 1 + 2:
+            problems.append(f'gate checked {sorted(report)}')
+        # the gate is sensitive to the adapter's row order: without the de-interleave it must object
+        wrong = dict(arm.results(state), dw_seg=state['dq'][1])
+        _, failures = bench.validate_step(
+            torch, dist, rank, world, hidden, heads,
+            dict(x=data['x'].detach(), grads=data['grads'], o=data['o'].detach(), dy=data['dy']), parameters,
+            wrong, bench.parity_tolerance('bf16', bias))
+        if not any('qkv_bwd dW' in f for f in failures):
+            problems.append('interleaved weight-gradient rows passed as segment-major')
+    finally:
+        undo()
+    queue.put((rank, problems))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('gate,bias', [(False, False), (True, True)])
+def test_fused_arm_adapter_passes_the_parity_gate_on_simulated_ranks(gate, bias):
+    world = 2
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=fused_arm_worker, args=(r, world, 29735 + gate, queue, gate, bias)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, problems in results:
+        assert problems == [], f'rank {rank}: {problems}'
