@@ -72,14 +72,28 @@ def gather(t):
 
 def main():
     local = int(os.environ['LOCAL_RANK'])
-    torch.cuda.set_device(local)
-    dev = torch.device('cuda', local)
-    dist.init_process_group('nccl', device_id=dev)
+    # FGA_DRIVER_SIMULATED=1 (the CPU test-suite): the same checks on gloo ranks with tests/abi_simulator.py
+    # in place of libfga.so, so that the driver itself - its geometries, gathers and expected values -
+    # has run before it meets a GPU. The CUDA-graph section needs a GPU and is skipped there.
+    simulated = os.environ.get('FGA_DRIVER_SIMULATED') == '1'
+    if simulated:
+        sys.path.insert(0, os.path.join(ROOT, 'tests'))
+        import abi_simulator
+        dev = torch.device('cpu')
+        dist.init_process_group('gloo')
+        torch.set_num_threads(2)
+        _, leave_simulation = abi_simulator.install(fused_gemm_a2a, abi_simulator.unique_tag())
+        device_sync = lambda: None      # noqa: E731
+    else:
+        torch.cuda.set_device(local)
+        dev = torch.device('cuda', local)
+        dist.init_process_group('nccl', device_id=dev)
+        device_sync = torch.cuda.synchronize
     fused_gemm_a2a.install_exit_guards()   # SIGTERM from the launcher: finish queued GPU work first
     rank, p = dist.get_rank(), dist.get_world_size()
     checks = 0
     verdict = Agreement(dev)
-    every_length = (300, 129, 1, 512, 255)
+    every_length = (129, 1) if simulated else (300, 129, 1, 512, 255)
     configurations = [(1024, 8, False, False, False, every_length), (1024, 8, True, True, False, every_length),
                       (1024, 8, False, True, True, every_length),
                       # the benchmark configurations' geometries (at CP = 8: 4 and 3 heads per rank), one length each
@@ -109,7 +123,7 @@ def main():
             dx, dwq, *dbq = torch.autograd.grad(outs, [x, wq_d] + ([bq_d] if with_bias else []), grads)
             y = proj(o, ws)
             do, dwo, *dbo = torch.autograd.grad(y, [o, wo_d] + ([bo_d] if with_bias else []), dy)
-            torch.cuda.synchronize()
+            device_sync()
             all_grads = list(zip(*[gather(t) for t in grads]))       # [rank][segment]
             all_o = gather(o.detach())
             xs, dys = gather(x.detach()), gather(dy)
@@ -154,7 +168,9 @@ def main():
         return torch.from_numpy(mx.mx_matmul(bits(a), bits(b))).to(BF)
 
     # (hidden 5120 with 40 heads is the MXFP8 benchmark configuration: 5 heads per rank at CP = 8)
-    for hidden, heads, lengths in ((1024, 8, (300, 129)), (5120, 40, (129,))):
+    # (simulated: 10 heads keep five heads per rank on two ranks; the float64 numpy products are the slow side)
+    mx_geometries = ((1024, 8, (129,)), (1280, 10, (129,))) if simulated else ((1024, 8, (300, 129)), (5120, 40, (129,)))
+    for hidden, heads, lengths in mx_geometries:
         d, hpr = hidden // heads, heads // p
         g = torch.Generator().manual_seed(99)
         wq = (torch.randn(3 * hidden, hidden, generator=g) / 32).to(BF)
@@ -173,7 +189,7 @@ def main():
             dx, dwq = torch.autograd.grad(outs, [x, wq_d], grads)
             y = proj(o, ws)
             do, dwo = torch.autograd.grad(y, [o, wo_d], dy)
-            torch.cuda.synchronize()
+            device_sync()
             xs, dys, all_o = gather(x.detach()), gather(dy), gather(o.detach())
             all_grads = list(zip(*[gather(t) for t in grads]))
             label = f'mxfp8 hidden={hidden} tokens={tokens}'
@@ -195,6 +211,13 @@ def main():
             verdict.settle(label)
     if rank == 0:
         print('PASS mxfp8', flush=True)
+
+    if simulated:
+        if rank == 0:
+            print(f'PASS simulated; {checks} eager configurations checked on {p} CPU ranks', flush=True)
+        leave_simulation()
+        dist.destroy_process_group()
+        return
 
     # CUDA graph: one captured step replayed with changed inputs
     hidden, heads, tokens, segments = 1024, 8, 333, 3

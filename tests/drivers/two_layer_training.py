@@ -139,7 +139,8 @@ def run(dev, hidden=1024, heads=8, total_tokens=512, replays=2):
                 failures.append(f'{stage}/{name}: {errors[f"{stage}/{name}"]}')
 
     def device_errors():
-        torch.cuda.synchronize()
+        if dev.type == 'cuda':
+            torch.cuda.synchronize()
         status = workspace.comm.status.tolist()
         if status[0]:
             failures.append(f'device status {status}')

@@ -32,7 +32,7 @@ import test_emulated_ranks as emulated  # noqa: E402
 from oracle import mxfp8_oracle as mx
 from oracle.ulysses_oracle import UlyssesOracle
 
-pytestmark = pytest.mark.gpu
+gpu = pytest.mark.gpu
 DEV = 'cuda:0'
 BF = torch.bfloat16
 
@@ -75,6 +75,7 @@ def inputs(hidden, heads, tokens, segments, with_bias, seed, weight_scale=None):
 
 def run_modules(case, ws, hidden, heads, gate, bias_in_gemm, main_grad=False):
     from fused_gemm_a2a import FusedOutputProjection, FusedQKVProjection
+    on_gpu = DEV != 'cpu'
     params = {name: (None if case[name] is None else torch.nn.Parameter(case[name].to(DEV)))
               for name in ('wq', 'wo', 'bq', 'bo')}
     seeds = {}
@@ -92,7 +93,8 @@ def run_modules(case, ws, hidden, heads, gate, bias_in_gemm, main_grad=False):
     o = case['o'].to(DEV).requires_grad_()
     y = proj(o, ws)
     y.backward(case['dy'].to(DEV))
-    torch.cuda.synchronize()
+    if on_gpu:
+        torch.cuda.synchronize()
     ws.comm.check_status()
     return dict(outs=outs, dx=x.grad, y=y, do=o.grad, params=params, seeds=seeds)
 
@@ -125,6 +127,7 @@ def check_bf16_case(case, got, hidden, heads, segments, bias_in_gemm, with_bias)
         close(got['params']['bo'].grad, dy32.sum(0).to(BF), 'dbias_o')
 
 
+@gpu
 def test_c2_c3_bf16_hidden_4096_32_heads_16384_tokens(cp1):
     from fused_gemm_a2a import FusedGemmA2AWorkspace
     hidden, heads, tokens = 4096, 32, 16384
@@ -134,6 +137,7 @@ def test_c2_c3_bf16_hidden_4096_32_heads_16384_tokens(cp1):
     check_bf16_case(case, got, hidden, heads, 3, False, False)
 
 
+@gpu
 def test_c4_gate_and_bias_hidden_3072_24_heads_odd_token_counts(cp1):
     """Three odd token counts from [4097, 8191] (seeded draw) share one workspace of capacity 8192;
     the bias is added by the GEMM epilogue for the first count and by the copy kernel for the others."""
@@ -158,6 +162,7 @@ def mm(a, b):
     return torch.from_numpy(mx.mx_matmul(bits(a), bits(b))).to(BF)
 
 
+@gpu
 def test_c5_mxfp8_hidden_5120_40_heads_outliers_zero_groups_main_grad(cp1):
     from fused_gemm_a2a import FusedGemmA2AWorkspace
     from fused_gemm_a2a_kernels import mxfp8_quantize
@@ -201,17 +206,20 @@ def test_c5_mxfp8_hidden_5120_40_heads_outliers_zero_groups_main_grad(cp1):
 
 
 # ---- the same geometries at CP = 8 on one GPU: 4, 3 and 5 heads per rank -------------------------
+@gpu
 @pytest.mark.parametrize('p,hidden,heads,tokens,segments,bias_in_gemm', [
     (8, 4096, 32, 129, 3, False), (8, 3072, 24, 77, 4, True), (8, 5120, 40, 129, 3, False)])
 def test_cp8_push_lands_in_the_right_peer_tiles(native, p, hidden, heads, tokens, segments, bias_in_gemm):
     emulated.test_push_lands_in_the_right_peer_tiles(native, p, hidden, heads, tokens, segments, bias_in_gemm)
 
 
+@gpu
 @pytest.mark.parametrize('p,hidden,heads,tokens', [(8, 4096, 32, 129), (8, 3072, 24, 77), (8, 5120, 40, 31)])
 def test_cp8_output_dgrad_push_routes_columns_to_their_owner(native, p, hidden, heads, tokens):
     emulated.test_output_dgrad_push_routes_columns_to_their_owner(native, p, hidden, heads, tokens)
 
 
+@gpu
 @pytest.mark.parametrize('p,hidden,heads,tokens,num_in', [
     (8, 4096, 32, 129, 3), (8, 4096, 32, 129, 1), (8, 3072, 24, 77, 4), (8, 3072, 24, 77, 1),
     (8, 5120, 40, 129, 3), (8, 5120, 40, 33, 1)])
@@ -220,6 +228,7 @@ def test_cp8_receive_transport_and_gemm(native, p, hidden, heads, tokens, num_in
 
 
 # ---- a matrix larger than 4 GiB -------------------------------------------------------------------
+@gpu
 def test_reduce_bias_grad_rows_beyond_four_gibibytes(native):
     """The last row of a [131073, 16384] BF16 matrix starts past 2^32 bytes and past 2^31 elements:
     row offsets must be 64-bit (reference tests/bias_grad_driver.py:54-59). Exact: one row of ones,
@@ -240,3 +249,64 @@ def test_reduce_bias_grad_rows_beyond_four_gibibytes(native):
     rc = native.fga_bias_grad_static(dy.data_ptr(), rows, width, out.data_ptr(), 0, 0,
                                      torch.cuda.current_stream().cuda_stream)
     assert rc == -1 and b'scratch floats' in native.fga_last_error()
+
+
+# ---- the checks themselves, on the CPU -----------------------------------------------------------
+def _simulated_worker(queue):
+    """This file's helpers (module run, row sampling, tile sampling, expected values) over the
+    simulated library on one CPU rank, at a small QKVG + bias geometry with a ragged last row block:
+    what the GPU tests above do, minus the GPU."""
+    import torch.distributed as dist
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.path.dirname(here)
+    for path in (here, root, os.path.join(root, 'fused-gemm-a2a_b200')):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT='29589')
+    dist.init_process_group('gloo', rank=0, world_size=1)
+    import abi_simulator
+    import fused_gemm_a2a as fused
+    import test_y_baseline_geometries as checks
+    checks.DEV = 'cpu'
+    _, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
+    problems = []
+    try:
+        hidden, heads = 768, 6
+        ws = fused.FusedGemmA2AWorkspace(hidden, heads, 1024, gate=True)
+        for index, tokens in enumerate((777, 513)):
+            case = checks.inputs(hidden, heads, tokens, 4, True, seed=40 + index, weight_scale=1 / 32)
+            got = checks.run_modules(case, ws, hidden, heads, gate=True, bias_in_gemm=index == 0)
+            try:
+                checks.check_bf16_case(case, got, hidden, heads, 4, index == 0, True)
+            except AssertionError as error:
+                problems.append(f'tokens={tokens}: {error}')
+            # and the checker does object: a weight gradient with two head blocks swapped
+            broken = got['params']['wq'].grad.clone()
+            broken[:128], broken[128:256] = got['params']['wq'].grad[128:256], got['params']['wq'].grad[:128]
+            got['params']['wq'].grad = broken
+            try:
+                checks.check_bf16_case(case, got, hidden, heads, 4, index == 0, True)
+                problems.append('swapped weight-gradient blocks were accepted')
+            except AssertionError:
+                pass
+    finally:
+        undo()
+    queue.put(problems)
+    dist.destroy_process_group()
+
+
+def test_the_sampled_checks_run_and_discriminate_on_the_simulated_library():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    proc = ctx.Process(target=_simulated_worker, args=(queue,))
+    proc.start()
+    try:
+        problems = queue.get(timeout=600)
+    finally:
+        proc.join(timeout=60)
+        if proc.is_alive():
+            proc.terminate()
+    assert problems == []
+    assert sampled_rows(8191).tolist()[::255][:3] == [0, 255, 3840 + 254] and len(sampled_rows(8191)) == 767
+    assert len(sampled_rows(100)) == 100 and sampled_tiles(12288, 3072)[1] == (12032, 2816)
