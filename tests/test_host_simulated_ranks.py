@@ -106,7 +106,8 @@ def run_rank(hidden, heads, capacity_tokens, token_counts, cases=None):
             proj = fused.FusedOutputProjection(hidden, heads, weight=params['wo'], bias=params['bo'])
             oracle = UlyssesOracle(p, hidden, heads, segments, wq, bq, wo, bo, bias_in_gemm=case['bias_in_gemm'])
             accumulated = {name: torch.zeros_like(t) for name, t in start.items()}
-            for tokens in (token_counts[1:2] if quantized and p > 2 else token_counts):
+            # the numpy MXFP8 oracle is the slow side: one rank alone runs every length, several ranks one
+            for tokens in (token_counts[1:2] if quantized and p > 1 else token_counts):
                 g = torch.Generator().manual_seed(1000 * tokens + rank)
                 x = torch.randn(tokens, hidden, generator=g).to(BF).requires_grad_()
                 grads = [torch.randn(p * tokens, heads // p, d, generator=g).to(BF) for _ in range(segments)]
