@@ -102,7 +102,7 @@ def test_timed_region_is_a_whole_number_of_requested_runs_and_long_enough():
     assert bench.timed_steps(3, 1e-4, 2.0) == 3000         # capped at 1000 repeats
 
 
-def test_link_bytes_follow_the_survey_table():
+def test_link_bytes_follow_the_all_to_all_payload_formula():
     """A2A payload per rank per pass M*N_out*2 B*(P-1)/P: 352.3 MB (QKV) and 117.4 MB (output) at CP = 8."""
     import bench
     per_step = bench.link_bytes_per_step(16384, 4096, 3, 8)
