@@ -430,6 +430,10 @@ class _Comm:
             if size < 0:
                 _native.check(-3)
             _native.check(lib.fga_symm_alloc_vmm(nbytes, ct.byref(local), ct.byref(descriptor)))
+            # The memory must also be usable as a tensor (torch looks the pointer up with the runtime
+            # before it adopts it): read the zero fill back through the same wrapper the slabs use.
+            if int(_wrap(local.value, min(nbytes, 4096), self.device).sum()) != 0:
+                raise RuntimeError('a fresh VMM allocation did not read back as zeros')
         except Exception as error:                 # noqa: BLE001  (the verdict must reach the all-reduce)
             problem = error
         seen, opened = [local.value], []          # opened: peers' memory mapped by this rank
