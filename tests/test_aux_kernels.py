@@ -1,9 +1,14 @@
 """GPU parity of the auxiliary kernels (row copy, bias gradient, MXFP8 quantizer) with the CPU
 oracle. Byte and index work is compared bit-exactly; FP32 sums by the reference's own bound
 4 * eps * sum|x| (tests/bias_grad_driver.py:23-46 of the reference)."""
+import os
+import sys
+
 import numpy as np
 import pytest
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from oracle import mxfp8_oracle as mx
 from oracle.ulysses_oracle import resize_rank_rows_ref
@@ -86,6 +91,45 @@ def test_reduce_bias_grad_integer_sums_are_exact(native):
     dy = torch.randint(-4, 5, (3000, 256)).to(torch.bfloat16)
     out = reduce_bias_grad(dy.to(DEV), torch.empty(256, dtype=torch.float32, device=DEV))
     assert torch.equal(out.cpu(), dy.float().sum(0))
+
+
+# ---- the reference's own Triton kernels, recorded through Triton's CPU interpreter ----------------
+@pytest.mark.parametrize('name', ['copy_grow', 'copy_shrink', 'copy_same', 'biased_grow', 'biased_shrink',
+                                  'biased_same'])
+def test_row_copy_equals_the_reference_kernels_recorded_output(native, name):
+    """tests/golden/aux_kernels.npz (made by tests/golden/make_golden_aux.py from
+    fused_gemm_a2a_kernels.py:1106-1142 of the reference): widths that are not multiples of 8, heads
+    of 16, 64 and 128 columns, head offsets, growing and shrinking. Bit for bit."""
+    from fused_gemm_a2a_kernels import resize_rank_rows
+    from test_oracle_golden import GOLDEN, aux_copy_case
+    z = np.load(os.path.join(GOLDEN, 'aux_kernels.npz'))
+    sources, wanted, peers, rows, kwargs = aux_copy_case(z, name)
+    if 'bias' in kwargs:
+        kwargs['bias'] = kwargs['bias'].to(DEV)
+    got = resize_rank_rows(tuple(t.to(DEV) for t in sources), peers, rows, copy=True, **kwargs)
+    for i, (a, w) in enumerate(zip(got, wanted)):
+        assert torch.equal(a.cpu().view(torch.int16), w.view(torch.int16)), f'{name} tensor {i}'
+
+
+@pytest.mark.parametrize('name', ['bias_one_part_bf16', 'bias_one_part_f32_acc', 'bias_parts_bf16_acc',
+                                  'bias_parts_f32', 'bias_many_parts_f32_acc'])
+def test_bias_gradient_against_the_reference_kernels_recorded_output(native, name):
+    """Same file, fused_gemm_a2a_kernels.py:1053-1103 of the reference. Both sides add in FP32 in
+    their own order: within twice the reference's bound 4 * eps * sum|x|; a BF16 result, which the
+    interpreter truncates, within one more BF16 step; the quarter-integer case bit for bit."""
+    from fused_gemm_a2a_kernels import reduce_bias_grad
+    from test_oracle_golden import GOLDEN, aux_tensor
+    z = np.load(os.path.join(GOLDEN, 'aux_kernels.npz'))
+    dy, previous, wanted = (aux_tensor(z, f'{name}.{key}') for key in ('dy', 'previous', 'out'))
+    accumulate = bool(z[f'{name}.accumulate'])
+    got = reduce_bias_grad(dy.to(DEV), previous.to(DEV).clone(), accumulate=accumulate).cpu()
+    if name == 'bias_many_parts_f32_acc':
+        assert torch.equal(got, wanted)
+        return
+    bound = 8 * torch.finfo(torch.float32).eps * (dy.double().abs().sum(0) + previous.double().abs() * accumulate)
+    if wanted.dtype == torch.bfloat16:
+        bound = bound + wanted.double().abs() * 2.0 ** -7
+    assert ((got.double() - wanted.double()).abs() <= bound + 1e-30).all()
 
 
 def _bits(t):

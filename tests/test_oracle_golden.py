@@ -171,3 +171,79 @@ def test_grouped_query_oracle_reproduces_reference_modules(name, kv_heads, gate,
     for r in range(p):
         padded = oracle.qkv_recv_buffer(grads, r, capacity)
         assert torch.equal(padded[:m], oracle.qkv_recv_buffer(grads, r)) and not padded[m:].any()
+
+
+# ---------------------------------------------------------------------- auxiliary kernels
+# tests/golden/aux_kernels.npz holds inputs and outputs of the reference's own Triton row-copy and
+# bias-gradient kernels (fused_gemm_a2a_kernels.py:1053-1142), executed by Triton's CPU interpreter
+# (tests/golden/make_golden_aux.py). BF16 tensors are stored as their uint16 bit patterns. The
+# interpreter narrows FP32 to BF16 by dropping bits where the compiled kernel rounds to nearest even,
+# so bit-exact cases use values whose results are exact in BF16, and the random-valued ones allow the
+# one BF16 step that the two narrowing rules can differ by.
+AUX_COPY_CASES = ('copy_grow', 'copy_shrink', 'copy_same', 'biased_grow', 'biased_shrink', 'biased_same')
+AUX_BIAS_CASES = ('bias_one_part_bf16', 'bias_one_part_f32_acc', 'bias_parts_bf16_acc', 'bias_parts_f32',
+                  'bias_many_parts_f32_acc')
+
+
+def aux_tensor(z, key):
+    a = z[key]
+    return torch.from_numpy(a.view(np.int16)).view(torch.bfloat16) if a.dtype == np.uint16 else torch.from_numpy(a)
+
+
+def aux_copy_case(z, name):
+    count = sum(1 for key in z.files if key.startswith(f'{name}.in'))
+    sources = tuple(aux_tensor(z, f'{name}.in{i}') for i in range(count))
+    wanted = tuple(aux_tensor(z, f'{name}.out{i}') for i in range(count))
+    kwargs = {}
+    if f'{name}.bias' in z.files:
+        kwargs = dict(bias=aux_tensor(z, f'{name}.bias'), head_dim=int(z[f'{name}.head_dim']),
+                      head_offset=int(z[f'{name}.head_offset']))
+    return sources, wanted, int(z[f'{name}.peers']), int(z[f'{name}.rows']), kwargs
+
+
+@pytest.mark.parametrize('name', AUX_COPY_CASES)
+def test_oracle_row_copy_is_the_reference_kernels_output_bit_for_bit(name):
+    from oracle.ulysses_oracle import resize_rank_rows_ref
+    z = np.load(os.path.join(GOLDEN, 'aux_kernels.npz'))
+    sources, wanted, peers, rows, kwargs = aux_copy_case(z, name)
+    got = resize_rank_rows_ref(sources, peers, rows, **kwargs)
+    for i, (a, w) in enumerate(zip(got, wanted)):
+        assert a.shape == w.shape and torch.equal(a.view(torch.int16), w.view(torch.int16)), f'{name} tensor {i}'
+
+
+def test_oracle_biased_row_copy_rounds_where_the_interpreter_truncates():
+    """Random values: the oracle rounds the FP32 sum to nearest even (what the reference's own check
+    demands, tests/row_copy_driver.py:40-57), the interpreted kernel drops the low bits. Wherever the
+    FP32 sum is exact in BF16 they are equal; elsewhere the recorded value is the next BF16 towards
+    zero or the oracle's own; rows past the input are zero in both."""
+    from oracle.ulysses_oracle import resize_rank_rows_ref
+    z = np.load(os.path.join(GOLDEN, 'aux_kernels.npz'))
+    sources, wanted, peers, rows, kwargs = aux_copy_case(z, 'biased_random')
+    got = resize_rank_rows_ref(sources, peers, rows, **kwargs)
+    in_rows = sources[0].shape[0] // peers
+    for a, w in zip(got, wanted):
+        a_bits, w_bits = a.view(torch.int16).int() & 0xffff, w.view(torch.int16).int() & 0xffff
+        assert ((a_bits == w_bits) | (a_bits == w_bits + 1)).all()   # same sign, magnitude at most one step up
+        assert (a_bits != w_bits).any()                              # the case does exercise the rounding
+        for t in (a, w):
+            assert not t.reshape(peers, rows, -1)[:, in_rows:].any()
+
+
+@pytest.mark.parametrize('name', AUX_BIAS_CASES)
+def test_oracle_bias_gradient_against_the_reference_kernels_output(name):
+    """The reference adds in FP32, 256 rows per partial sum, the oracle in FP64: they agree within
+    the reference's own bound 4 * eps * sum|x| (tests/bias_grad_driver.py:23-46 of the reference) plus,
+    for a BF16 result, one rounding. The quarter-integer case has exact FP32 sums: bit-exact."""
+    from oracle.ulysses_oracle import reduce_bias_grad_ref
+    z = np.load(os.path.join(GOLDEN, 'aux_kernels.npz'))
+    dy, previous, wanted = (aux_tensor(z, f'{name}.{key}') for key in ('dy', 'previous', 'out'))
+    accumulate = bool(z[f'{name}.accumulate'])
+    got = reduce_bias_grad_ref(dy, wanted.dtype, previous=previous if accumulate else None)
+    if name == 'bias_many_parts_f32_acc':
+        # exact column sums, then one FP32 addition of the previous value: nothing depends on the order
+        assert torch.equal(wanted, dy.double().sum(0).float() + previous)
+        assert torch.equal(got, wanted)
+    bound = 4 * torch.finfo(torch.float32).eps * (dy.double().abs().sum(0) + previous.double().abs() * accumulate)
+    if wanted.dtype == torch.bfloat16:
+        bound = bound + wanted.double().abs() * 2.0 ** -7   # rounded here, truncated by the interpreter
+    assert ((got.double() - wanted.double()).abs() <= bound + 1e-30).all(), name
