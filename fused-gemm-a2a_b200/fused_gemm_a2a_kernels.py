@@ -265,15 +265,19 @@ def mxfp8_wgrad(dy, x, out, *, accumulate=False, status=None):
     transposed) and multiplied by the block-scaled GEMM; FP32 outputs may accumulate in place
     (reference fused_gemm_a2a_kernels.py:1398-1421). `status` is the device status word that a
     bounded wait reports to; without one a per-device word is used, which _Comm.check_status() and
-    clear_status() of any group on that device also cover."""
+    clear_status() of any group on that device also cover. Returns the object that stands for the
+    launched kernel (see _InlinePtx below), as the reference does."""
     if accumulate and out.dtype != torch.float32:
         raise ValueError('MXFP8 gradient accumulation requires FP32 output')
     if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous():
         raise ValueError('MXFP8 weight gradient needs a contiguous BF16 or FP32 output')
     dq, ds = mxfp8_quantize(dy.T)
     xq, xs = mxfp8_quantize(x.T)
-    return mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1],
-                      _status_word(out.device) if status is None else status, accumulate=accumulate)
+    mxfp8_gemm(dq, ds, xq, xs, out, out.shape[0], out.shape[1],
+               _status_word(out.device) if status is None else status, accumulate=accumulate)
+    # The reference returns the kernel it launched, and its acceptance driver reads that object's
+    # `__ptx__` (tests/mxfp8_driver.py:239-244 of the reference); the result itself is in `out`.
+    return _native_mxfp8_kernels[0] if _native_mxfp8_kernels else None
 
 
 class _InlinePtx:

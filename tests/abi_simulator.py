@@ -31,6 +31,21 @@ from host_trace import _TorchShim   # torch as seen from inside the package: the
 
 BF16 = torch.bfloat16
 
+# When set (tests/cuda_stage.py sets it while it emulates the capture of a CUDA graph), every simulated
+# kernel launch goes through it as launch_hook(function, args, kwargs): a launch is one node of the
+# recorded graph and is run again, with the same raw arguments, on every replay.
+launch_hook = None
+
+
+def _as_launch(function):
+    def call(*args, **kwargs):
+        if launch_hook is not None:
+            return launch_hook(function, args, kwargs)
+        return function(*args, **kwargs)
+    call.__name__ = getattr(function, '__name__', 'launch')
+    call.__wrapped__ = function
+    return call
+
 
 def _bytes_at(address, nbytes):
     return (ctypes.c_char * nbytes).from_address(int(address))
@@ -59,13 +74,16 @@ def mx_product(a, b):
 class SimulatedLibrary:
     def __init__(self, tag):
         self.tag = tag                    # unique per test run: names of the shared segments
-        self.rank = dist.get_rank()
         self.segments = []                # SharedMemory objects this process created or opened
         self.created = []
         self.launches = 0
         self.quantized = []               # (payload tensor, BF16 matrix it was quantized from), kept alive
         self.mappings = []                # memory-mapped descriptors of the VMM flavour
         self.released = []                # what the host layer gave back, in order
+
+    @property
+    def rank(self):
+        return dist.get_rank()            # asked late: the library may be installed before the group exists
 
     def source_of(self, address):
         for payload, source in reversed(self.quantized):
@@ -149,6 +167,80 @@ class SimulatedLibrary:
             except FileNotFoundError:
                 pass
 
+    # ---- kernels without an exchange, on the raw bytes the header describes. The host layer's
+    # projections reach these through wrappers that install() replaces wholesale; a program that
+    # imports the wrappers from fused_gemm_a2a_kernels itself (tests/cuda_stage.py) lands here.
+    @staticmethod
+    def _strided(address, rows, cols, pitch, dtype):
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        flat = torch.frombuffer(_bytes_at(address, ((rows - 1) * pitch + cols) * itemsize), dtype=dtype)
+        return torch.as_strided(flat, (rows, cols), (pitch, 1))
+
+    @_as_launch
+    def fga_mx_quantize(self, a, rows, k, stride_row, stride_k, q, sf, rows_padded, k_padded, stream):
+        from oracle import mxfp8_oracle
+        self.launches += 1
+        extent = (rows - 1) * stride_row + (k - 1) * stride_k + 1
+        logical = torch.as_strided(torch.frombuffer(_bytes_at(a, extent * 2), dtype=BF16), (rows, k),
+                                   (stride_row, stride_k))
+        payload, scales = mxfp8_oracle.quantize(bf16_bits(logical), k_multiple=k_padded, row_multiple=rows_padded)
+        assert payload.shape == (rows_padded, k_padded)
+        torch.frombuffer(_bytes_at(q, rows_padded * k_padded), dtype=torch.uint8).copy_(
+            torch.from_numpy(payload).reshape(-1))
+        torch.frombuffer(_bytes_at(sf, rows_padded * k_padded // 32), dtype=torch.uint8).copy_(torch.from_numpy(scales))
+        return 0
+
+    @_as_launch
+    def fga_gemm_local_mx(self, aq, sfa, a_rows_padded, bq, sfb, b_rows_padded, m, n, kp, c, ldc, out_f32, accumulate,
+                          status, timeout, stream):
+        from oracle import mxfp8_oracle
+        self.launches += 1
+
+        def values(payload, scales, rows):
+            raw = torch.frombuffer(_bytes_at(payload, rows * kp), dtype=torch.uint8).numpy().reshape(rows, kp)
+            factors = torch.frombuffer(_bytes_at(scales, rows * kp // 32), dtype=torch.uint8).numpy()
+            return torch.from_numpy(mxfp8_oracle.dequantize(raw, factors, rows, kp).reshape(rows, kp))
+
+        product = (values(aq, sfa, a_rows_padded)[:m] @ values(bq, sfb, b_rows_padded)[:n].t()).float()
+        out = self._strided(c, m, n, ldc, torch.float32 if out_f32 else BF16)
+        out.copy_(out + product if accumulate else product)
+        return 0
+
+    @_as_launch
+    def fga_gemm_local(self, a, a_is_km, b, b_is_kn, m, n, k, lda, ldb, c, ldc, out_f32, accumulate, status, timeout,
+                       stream):
+        self.launches += 1
+        left = self._strided(a, k, m, lda, BF16).t() if a_is_km else self._strided(a, m, k, lda, BF16)
+        right = self._strided(b, k, n, ldb, BF16).t() if b_is_kn else self._strided(b, n, k, ldb, BF16)
+        product = left.float() @ right.float().t()
+        out = self._strided(c, m, n, ldc, torch.float32 if out_f32 else BF16)
+        out.copy_(out + product if accumulate else product)
+        return 0
+
+    @_as_launch
+    def fga_copy_rank_rows(self, sources, outputs, segments, peers, rows_in, rows_out, width, bias, head_dim,
+                           head_offset, stream):
+        from oracle.ulysses_oracle import resize_rank_rows_ref
+        self.launches += 1
+        tensors = tuple(matrix(sources[i], peers * rows_in, width) for i in range(segments))
+        covered = (head_offset * head_dim + width) * segments
+        results = resize_rank_rows_ref(tensors, peers, rows_out, head_dim=head_dim, head_offset=head_offset,
+                                       bias=matrix(bias, 1, covered)[0] if bias else None)
+        for i, result in enumerate(results):
+            matrix(outputs[i], peers * rows_out, width).copy_(result)
+        return 0
+
+    def fga_bias_grad_scratch_floats(self, rows, width):
+        return -(-rows // 256) * width
+
+    @_as_launch
+    def fga_bias_grad(self, dy, rows, width, out, out_is_f32, accumulate, scratch, stream):
+        from oracle.ulysses_oracle import reduce_bias_grad_ref
+        self.launches += 1
+        target = matrix(out, 1, width, torch.float32 if out_is_f32 else BF16)[0]
+        target.copy_(reduce_bias_grad_ref(matrix(dy, rows, width), target.dtype, previous=target if accumulate else None))
+        return 0
+
     # ---- fused GEMMs (contract: include/fga.h)
     def _route_push(self, product, a_rows, segments, n_segment, tables, head_rows, rank, p):
         """Store a [a_rows, segments*n_segment] BF16 result unit by unit (128 columns = one head of one
@@ -161,6 +253,7 @@ class SimulatedLibrary:
             target[rank * head_rows:rank * head_rows + a_rows, within * 128:(within + 1) * 128] = \
                 product[:, unit * 128:(unit + 1) * 128]
 
+    @_as_launch
     def fga_gemm_push(self, a, m, k, a_rows, b, b_is_kn, bias, segments, n_segment, tables, head_rows,
                       rank, p, status, timeout, stream):
         self.launches += 1
@@ -174,6 +267,7 @@ class SimulatedLibrary:
         self._route_push(product.to(BF16), a_rows, segments, n_segment, tables, head_rows, rank, p)
         return 0
 
+    @_as_launch
     def fga_gemm_push_mx(self, aq, sfa, a_rows_padded, kp, a_rows, bq, sfb, b_rows_padded, bias, segments,
                          n_segment, tables, head_rows, rank, p, status, timeout, stream):
         self.launches += 1
@@ -215,6 +309,7 @@ class SimulatedLibrary:
         own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
         return not roles & 2 or bool((own == expected).all())
 
+    @_as_launch
     def fga_gemm_recv(self, recv, recv_rows, k, b, b_is_kn, n, c, peer_recv, peer_counters, counters,
                       srcs, num_in, src_rows, split, rank, p, roles, epoch, progress, status, timeout, stream):
         self.launches += 1
@@ -232,6 +327,7 @@ class SimulatedLibrary:
         """(first unit, units) of q, k, v(, gate) inside one key/value group."""
         return [(0, q_per_kv), (q_per_kv, 1), (q_per_kv + 1, 1)] + ([(q_per_kv + 2, q_per_kv)] if gate else [])
 
+    @_as_launch
     def fga_gemm_push_gqa(self, a, m, k, a_rows, b, bias, kv_heads, q_per_kv, gate, tables, head_rows, rank, p,
                           status, timeout, stream):
         self.launches += 1
@@ -254,6 +350,7 @@ class SimulatedLibrary:
             target[rank * head_rows:rank * head_rows + a_rows, column:column + 128] = product[:, unit * 128:(unit + 1) * 128]
         return 0
 
+    @_as_launch
     def fga_gemm_recv_gqa(self, recv, recv_rows, b, n, c, peer_recv, peer_counters, counters, srcs, kv_heads, q_per_kv,
                           gate, src_rows, split, rank, p, roles, progress, status, timeout, stream):
         self.launches += 1
@@ -286,6 +383,7 @@ class SimulatedLibrary:
             matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ matrix(b, k, n).float()).to(BF16)
         return 0
 
+    @_as_launch
     def fga_gemm_recv_mx(self, recv, mx_recv, mx_scale, recv_rows, k, bq, sfb, b_rows_padded, b_kp, n, c,
                          peer_recv, peer_counters, counters, srcs, num_in, src_rows, split, rank, p, roles,
                          epoch, progress, status, timeout, stream):
@@ -359,8 +457,20 @@ def install(fused, tag):
         out.copy_((out.float() + product) if accumulate else product)
         return out
 
+    def requantized(old_outputs, new_outputs):
+        # A replayed quantizer launch: its payload tensor stays the one recorded, so the BF16 matrix that
+        # the later GEMM launches look up by that address takes the new values.
+        _, fresh = sim.quantized.pop()
+        for payload, source in sim.quantized:
+            if payload.data_ptr() == old_outputs[0].data_ptr():
+                source.copy_(fresh)
+    mxfp8_quantize.after_replay = requantized
+
     for fn in (device_barrier, resize_rank_rows, reduce_bias_grad, bf16_wgrad, mxfp8_quantize, mxfp8_wgrad):
-        setattr(fused, fn.__name__, fn)
+        launch = _as_launch(fn)
+        if hasattr(fn, 'after_replay'):
+            launch.after_replay = fn.after_replay
+        setattr(fused, fn.__name__, launch)
 
     def undo(meet=True):
         sim.close(meet)

@@ -4,6 +4,13 @@ import sys
 
 import pytest
 
+# Several CPU tests run two to four ranks of torch work on the same cores. OpenMP workers that spin
+# while they wait for the next parallel region then steal the cores from the other ranks; let them
+# sleep instead. Read when the OpenMP runtime starts, so set before anything imports torch; child
+# processes inherit it.
+os.environ.setdefault('OMP_WAIT_POLICY', 'PASSIVE')
+os.environ.setdefault('GOMP_SPINCOUNT', '0')
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PACKAGE = os.path.join(ROOT, 'fused-gemm-a2a_b200')
 for path in (ROOT, PACKAGE):

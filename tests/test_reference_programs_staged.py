@@ -1,0 +1,95 @@
+"""The reference project's own acceptance drivers and benchmark harness, unmodified, against this
+package on CPU ranks.
+
+oracle/build_ref.py stages byte-identical copies of those programs under oracle/_ref/ (a git-ignored
+build output); tests/cuda_stage.py runs a program written for CUDA devices in processes without a GPU
+(devices rewritten to the CPU, torch.cuda stand-ins, an emulation of CUDA-graph capture and replay)
+with libfga.so replaced by tests/abi_simulator.py. What passes here is everything those programs demand
+of the host layer: names and signatures, error messages, frozen configuration, cached views, "no
+allocation, synchronization or group barrier after set-up", ownership of returned tensors, the
+main_grad protocol, saved-tensor hooks, micro-batches of different lengths with delayed backward,
+pipeline-parallel set-up order, and correct values after graph replays with changed inputs - checked
+by the reference's own independent FP32 computations. It says nothing about the CUDA kernels;
+tests/test_zu_reference_drivers.py runs the same programs on GPUs.
+
+All programs are started together when the first test asks for one (they are independent processes
+with two threads each), so the file costs about as long as its slowest program. FGA_STAGED=all adds the
+long ones (minutes each on eight cores).
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+STAGED = os.path.join(ROOT, 'oracle', '_ref')
+STAGE = os.path.join(ROOT, 'tests', 'cuda_stage.py')
+pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(STAGED, 'benchmark', 'run.py')),
+                                reason='oracle/_ref/ has not been built (no reference tree at build time)')
+
+HARNESS = ('--tokens', '512', '--hidden-size', '1024', '--heads', '8', '--iterations', '2', '--trials', '1',
+           '--warmup', '1', '--graph-batch', '2', '--layers', '2', '--cuda-graphs', '--validation-rounds', '2')
+# name: (ranks, stage flags, program, arguments, line the program prints on success, runs by default)
+PROGRAMS = {
+    'harness_bf16_cp2': (2, (), 'benchmark/run.py', ('--cp', '2', *HARNESS, '--bias', '--bias-in-gemm', '--gate'),
+                         'Validation passed', True),
+    'harness_mxfp8_cp1': (1, (), 'benchmark/run.py',
+                          ('--cp', '1', '--tokens', '256', '--hidden-size', '512', '--heads', '4', '--iterations', '1',
+                           '--trials', '1', '--warmup', '1', '--graph-batch', '1', '--layers', '2', '--cuda-graphs',
+                           '--validation-rounds', '1', '--precision', 'mxfp8'), 'Validation passed', True),
+    'pipeline_setup': (4, (), 'tests/pipeline_setup_driver.py', ('--prepare',), 'PIPELINE_SETUP_PASS', True),
+    'attention_training': (1, ('--stand-in-attention',), 'tests/attention_training_driver.py', ('--tokens', '256'),
+                           'checks passed with owned QKV outputs', True),
+    'recv_padding': (1, (), 'tests/recv_padding_driver.py', (), 'PASS receive padding: segments=4', True),
+    'mxfp8_modules': (1, (), 'tests/mxfp8_driver.py', ('--heads', '2', '--lengths', '33', '257'), 'MXFP8_PASS', True),
+    'mxfp8_local': (1, (), 'tests/mxfp8_local_driver.py', (), 'MXFP8_LOCAL_PASS', True),
+    'variable_length': (1, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
+                        ('--local-tokens', '130', '1', '257'), 'Variable-length projections', False),
+    'variable_length_cp2': (2, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
+                            ('--local-tokens', '130', '1'), 'Variable-length projections', False),
+    'attention_training_cp2': (2, ('--stand-in-attention',), 'tests/attention_training_driver.py',
+                               ('--tokens', '256'), 'checks passed with owned QKV outputs', False),
+    'harness_bf16_cp4': (4, (), 'benchmark/run.py', ('--cp', '4', *HARNESS), 'Validation passed', False),
+}
+NEEDS_OUTPUT = {'benchmark/run.py', 'tests/attention_training_driver.py', 'tests/recv_padding_driver.py',
+                'tests/mxfp8_driver.py', 'tests/mxfp8_local_driver.py', 'tests/variable_length_driver.py'}
+
+
+def selected():
+    everything = os.environ.get('FGA_STAGED', '') == 'all'
+    return [name for name, spec in PROGRAMS.items() if spec[-1] or everything]
+
+
+@pytest.fixture(scope='module')
+def running(tmp_path_factory):
+    """Every selected program as a process tree of its own, all started now."""
+    scratch = tmp_path_factory.mktemp('staged')
+    env = dict(os.environ, FGA_STAGE_THREADS='2')
+    started = {}
+    for index, name in enumerate(selected()):
+        ranks, flags, program, arguments, _, _ = PROGRAMS[name]
+        command = [sys.executable, STAGE, '--ranks', str(ranks), '--port', str(29700 + index), *flags,
+                   os.path.join(STAGED, program), *arguments]
+        if program in NEEDS_OUTPUT:
+            command += ['--output', str(scratch / f'{name}.json')]
+        started[name] = subprocess.Popen(command, env=env, cwd=ROOT, stdout=subprocess.PIPE,
+                                         stderr=subprocess.STDOUT, text=True)
+    yield started
+    for process in started.values():
+        if process.poll() is None:
+            process.kill()
+            process.communicate()
+
+
+@pytest.mark.parametrize('name', selected())
+def test_reference_program_passes_on_the_cpu_stage(running, name):
+    process = running[name]
+    try:
+        output, _ = process.communicate(timeout=3000)
+    except subprocess.TimeoutExpired:
+        process.kill()
+        output, _ = process.communicate()
+        pytest.fail(f'{name}: no end after 3000 s\n{output[-3000:]}')
+    assert process.returncode == 0, f'{name} exited {process.returncode}\n{output[-4000:]}'
+    assert PROGRAMS[name][4] in output, output[-2000:]
