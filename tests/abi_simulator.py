@@ -37,6 +37,13 @@ BF16 = torch.bfloat16
 launch_hook = None
 
 
+def _meet():
+    """Where the simulated ranks must meet. A single process that plays every rank in turn (the
+    one-device rank emulation of the GPU tests) has nobody to wait for."""
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
 def _as_launch(function):
     def call(*args, **kwargs):
         if launch_hook is not None:
@@ -153,7 +160,7 @@ class SimulatedLibrary:
 
     def close(self, meet=True):
         if meet:
-            dist.barrier()             # nobody unmaps while a peer may still store into the segment
+            _meet()             # nobody unmaps while a peer may still store into the segment
         self.segments.clear()
         import gc
         gc.collect()
@@ -288,7 +295,7 @@ class SimulatedLibrary:
             # One rank pushes at a time: the counter increments below are plain read-modify-writes
             # on memory that every rank maps (the GPU uses atomic reductions).
             if turn != rank:
-                dist.barrier()
+                _meet()
                 continue
             for dest in range(p):
                 target = matrix(table(peer_recv, p)[dest], recv_rows, k)
@@ -301,9 +308,9 @@ class SimulatedLibrary:
                         target[:src_rows, column:column + 128] = source[:, unit * 128:(unit + 1) * 128]
                         target[src_rows:, column:column + 128] = 0
                     arrivals += split          # `split` jobs per (row block, source, destination)
-            dist.barrier()                     # after the last turn: every row block has all its arrivals
+            _meet()                     # after the last turn: every row block has all its arrivals
         if not roles & 2:
-            dist.barrier()
+            _meet()
 
     def _arrived(self, counters, recv_rows, expected, roles):
         own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
@@ -359,7 +366,7 @@ class SimulatedLibrary:
         k = kv_heads * per_group * 128
         for turn in range(p if roles & 2 else 0):
             if turn != rank:
-                dist.barrier()
+                _meet()
                 continue
             for dest in range(p):
                 target = matrix(table(peer_recv, p)[dest], recv_rows, k)
@@ -374,9 +381,9 @@ class SimulatedLibrary:
                         target[:src_rows, column:column + 128] = source[:, unit * 128:(unit + 1) * 128]
                         target[src_rows:, column:column + 128] = 0
                     arrivals += split
-            dist.barrier()
+            _meet()
         if not roles & 2:
-            dist.barrier()
+            _meet()
         if roles & 1:
             if not self._arrived(counters, recv_rows, p * len(kinds) * split, roles):
                 return -2

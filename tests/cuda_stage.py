@@ -9,7 +9,7 @@ behaviour under graph replay with changed inputs - is exercised before a GPU eve
 here says anything about the kernels.
 
     python tests/cuda_stage.py [--ranks N] [--port P] [--cpu-is-elsewhere] [--stand-in-attention]
-                               <script.py> [script arguments...]
+                               (<script.py> | -m <module>) [arguments...]
 
 One process per rank: with --ranks N this file starts N copies of itself with RANK / LOCAL_RANK /
 WORLD_SIZE / MASTER_ADDR / MASTER_PORT set (a launcher may also set them itself). What the stage
@@ -376,7 +376,7 @@ def main():
     arguments = sys.argv[1:]
     options = dict(ranks=1, port=29690, timeout=1500)
     flags = []
-    while arguments and arguments[0].startswith('--'):
+    while arguments and arguments[0].startswith('--'):   # the stage's own options come first
         flag = arguments.pop(0)
         if flag in ('--cpu-is-elsewhere', '--stand-in-attention'):
             flags.append(flag)
@@ -398,6 +398,10 @@ def main():
     if '--stand-in-attention' in flags:
         _stand_in_attention()
     _stand_in_scaled_mm()
+    if arguments[0] == '-m':                       # a module, as in `python -m pytest ...`
+        sys.argv = arguments[1:]
+        runpy.run_module(arguments[1], run_name='__main__', alter_sys=True)
+        return
     sys.argv = arguments
     STATE.program = os.path.abspath(arguments[0])
     runpy.run_path(arguments[0], run_name='__main__')

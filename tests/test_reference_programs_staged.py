@@ -1,5 +1,5 @@
 """The reference project's own acceptance drivers and benchmark harness, unmodified, against this
-package on CPU ranks.
+package on CPU ranks - and this repository's own GPU test files over the same stage.
 
 oracle/build_ref.py stages byte-identical copies of those programs under oracle/_ref/ (a git-ignored
 build output); tests/cuda_stage.py runs a program written for CUDA devices in processes without a GPU
@@ -44,6 +44,17 @@ PROGRAMS = {
     'recv_padding': (1, (), 'tests/recv_padding_driver.py', (), 'PASS receive padding: segments=4', True),
     'mxfp8_modules': (1, (), 'tests/mxfp8_driver.py', ('--heads', '2', '--lengths', '33', '257'), 'MXFP8_PASS', True),
     'mxfp8_local': (1, (), 'tests/mxfp8_local_driver.py', (), 'MXFP8_LOCAL_PASS', True),
+    # This repository's own GPU test files (their host logic: shapes, call sequences, expectations against
+    # the oracle) over the same stage, so that no GPU test meets a GPU with its own code unrun. Left out:
+    # what only the real library can answer (argument validation, bounded device waits, the static
+    # scratch array) and the files that start GPU processes of their own.
+    'own_gpu_tests': (1, (), '-m', ('pytest', '-q', '-m', 'gpu', '-p', 'no:cacheprovider', 'tests/test_emulated_ranks.py',
+                                   'tests/test_fused_modules.py', 'tests/test_gemm_local.py', 'tests/test_mxfp8_gemm.py',
+                                   'tests/test_mxfp8_modules.py', 'tests/test_yb_grouped_query.py',
+                                   'tests/test_zx_two_layer_training.py', 'tests/test_zy_opt_in_paths.py',
+                                   'tests/test_aux_kernels.py', '-k',
+                                   'not test_argument_validation and not test_argument_errors_are_reported '
+                                   'and not rejects_bad_arguments'), ' passed', True),
     'variable_length': (1, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
                         ('--local-tokens', '130', '1', '257'), 'Variable-length projections', False),
     'variable_length_cp2': (2, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
@@ -70,7 +81,7 @@ def running(tmp_path_factory):
     for index, name in enumerate(selected()):
         ranks, flags, program, arguments, _, _ = PROGRAMS[name]
         command = [sys.executable, STAGE, '--ranks', str(ranks), '--port', str(29700 + index), *flags,
-                   os.path.join(STAGED, program), *arguments]
+                   program if program == '-m' else os.path.join(STAGED, program), *arguments]
         if program in NEEDS_OUTPUT:
             command += ['--output', str(scratch / f'{name}.json')]
         started[name] = subprocess.Popen(command, env=env, cwd=ROOT, stdout=subprocess.PIPE,
@@ -93,3 +104,4 @@ def test_reference_program_passes_on_the_cpu_stage(running, name):
         pytest.fail(f'{name}: no end after 3000 s\n{output[-3000:]}')
     assert process.returncode == 0, f'{name} exited {process.returncode}\n{output[-4000:]}'
     assert PROGRAMS[name][4] in output, output[-2000:]
+    assert ' failed' not in output.splitlines()[-1], output[-2000:]
