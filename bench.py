@@ -61,12 +61,16 @@ DRAM_BYTES_PER_FLOP = dict(gemm=670.4e6 / 824.6e9, wgrad=1296.8e6 / 824.6e9)
 PARITY_TOLERANCE = dict(bf16=(1e-2, 2e-3), mxfp8=(2.5e-1, 8e-2))
 
 
-def parity_tolerance(precision, bias):
+def parity_tolerance(precision, bias, unfused=False):
     """The gate's bound for a run. With a bias the projections round to BF16 twice (GEMM result, then
     the bias add) while the gate's FP32 reference rounds never, which puts the relative Frobenius error
     of a correct BF16 result at about 2.3e-3 (sqrt(2) times a single rounding); the test-suite's oracle
-    models that double rounding, the gate allows for it."""
+    models that double rounding, the gate allows for it. The unfused comparison arm rounds more often
+    still: its dX is the BF16 sum of three or four separately rounded BF16 products (one per
+    projection), which measures 2.9e-3 to 3.2e-3 on correct results, so that arm gets twice the bound."""
     worst, frobenius = PARITY_TOLERANCE[precision]
+    if unfused:
+        return worst, frobenius * 2.0
     return (worst, frobenius * 1.5) if bias and precision == 'bf16' else (worst, frobenius)
 
 
@@ -871,7 +875,8 @@ def run_gpu_arm(args):
         if not args.no_validate:
             # Nothing is timed before one step's results have been checked; a mismatch on any rank
             # ends the run on every rank (nobody leaves alone).
-            tolerance = parity_tolerance(args.precision if args.impl == 'fused' else 'bf16', args.bias)
+            tolerance = parity_tolerance(args.precision if args.impl == 'fused' else 'bf16', args.bias,
+                                         unfused=args.impl != 'fused')
             report, failures = validate_step(
                 torch, dist, rank, p, hidden, heads, dict(x=x.detach(), grads=grads, o=o.detach(), dy=dy),
                 dict(w_seg=w_seg, wo=wo, bq=bq, bo=bo), results(), tolerance)

@@ -98,6 +98,9 @@ class SimulatedLibrary:
                 return source
         raise KeyError('operand was not produced by the quantizer wrapper')
 
+    def fga_launch_count(self):
+        return self.launches
+
     def fga_last_error(self):
         return b'simulated library: a receive row block did not collect all of its arrivals'
 

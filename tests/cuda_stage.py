@@ -256,6 +256,13 @@ CUDA_STAND_INS = dict(
     mem_get_info=lambda device=None: (170 << 30, 180 << 30))
 
 
+class _HostGenerator(torch.Generator):
+    """torch.Generator is a class, so the function mode never sees its constructor's device."""
+
+    def __new__(cls, device='cpu'):
+        return super().__new__(cls, 'cpu')
+
+
 class _PackageCuda:
     @staticmethod
     def current_device():
@@ -294,6 +301,7 @@ def install(cpu_is_elsewhere=False):
     for name, stand_in in CUDA_STAND_INS.items():
         setattr(torch.cuda, name, stand_in)
     dist.init_process_group = _init_process_group(dist.init_process_group)
+    torch.Generator = _HostGenerator
     _, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
     # The package's own view of torch: the CPU is "the device" (its index is None), and every torch.cuda
     # call goes to the stand-ins above through the real module, so that a program which patches

@@ -30,6 +30,8 @@ pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(STAGED, 'benchma
 
 HARNESS = ('--tokens', '512', '--hidden-size', '1024', '--heads', '8', '--iterations', '2', '--trials', '1',
            '--warmup', '1', '--graph-batch', '2', '--layers', '2', '--cuda-graphs', '--validation-rounds', '2')
+BENCH = ('--steps', '2', '--warmup', '1', '--tokens', '512', '--hidden', '1024', '--heads', '8', '--min-seconds', '0.2',
+         '--cpu-sample-tokens', '256')
 # name: (ranks, stage flags, program, arguments, line the program prints on success, runs by default)
 PROGRAMS = {
     'harness_bf16_cp2': (2, (), 'benchmark/run.py', ('--cp', '2', *HARNESS, '--bias', '--bias-in-gemm', '--gate'),
@@ -55,6 +57,13 @@ PROGRAMS = {
                                    'tests/test_aux_kernels.py', '-k',
                                    'not test_argument_validation and not test_argument_errors_are_reported '
                                    'and not rejects_bad_arguments'), ' passed', True),
+    # bench.py's GPU code path itself (CUDA events, graphs, copy streams, the parity gate, the instrumented
+    # steps, the JSON line) rather than its --device cpu harness mode.
+    'bench_fused': (1, (), 'bench.py', BENCH, '"roofline"', True),
+    'bench_unfused_cp2': (2, (), 'bench.py', (*BENCH, '--gpus', '2', '--impl', 'nccl', '--no-e2e'), '"parity_check"', True),
+    'bench_mxfp8': (1, (), 'bench.py', ('--steps', '1', '--warmup', '1', '--tokens', '256', '--hidden', '512', '--heads', '4',
+                                        '--min-seconds', '0.05', '--precision', 'mxfp8', '--no-e2e', '--no-cpu-baseline'),
+                    '"roofline"', True),
     'variable_length': (1, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
                         ('--local-tokens', '130', '1', '257'), 'Variable-length projections', False),
     'variable_length_cp2': (2, ('--cpu-is-elsewhere',), 'tests/variable_length_driver.py',
@@ -81,7 +90,8 @@ def running(tmp_path_factory):
     for index, name in enumerate(selected()):
         ranks, flags, program, arguments, _, _ = PROGRAMS[name]
         command = [sys.executable, STAGE, '--ranks', str(ranks), '--port', str(29700 + index), *flags,
-                   program if program == '-m' else os.path.join(STAGED, program), *arguments]
+                   program if program == '-m' else os.path.join(ROOT if program == 'bench.py' else STAGED, program),
+                   *arguments]
         if program in NEEDS_OUTPUT:
             command += ['--output', str(scratch / f'{name}.json')]
         started[name] = subprocess.Popen(command, env=env, cwd=ROOT, stdout=subprocess.PIPE,
@@ -105,3 +115,12 @@ def test_reference_program_passes_on_the_cpu_stage(running, name):
     assert process.returncode == 0, f'{name} exited {process.returncode}\n{output[-4000:]}'
     assert PROGRAMS[name][4] in output, output[-2000:]
     assert ' failed' not in output.splitlines()[-1], output[-2000:]
+    if PROGRAMS[name][2] == 'bench.py':
+        import json
+        line = json.loads([text for text in output.splitlines() if text.startswith('{')][-1])
+        assert line['parity_check']['passed'] and line['value'] > 0
+        assert (line['gpu_launches'] > 0) == (line['impl'] == 'fused')   # only this repository's kernels count
+        assert 'graph' in line['config']['launch'] and 'failed' not in line['config']['launch'], line['config']['launch']
+        if name == 'bench_fused':
+            assert line['e2e']['h2d_bytes_per_step'] > 0 and line['e2e']['d2h_bytes_per_step'] > 0
+            assert line['cpu_baseline']['kind'] == 'reference' and line['roofline']['launches_timed'] > 0
