@@ -23,7 +23,9 @@ provides:
     exact product of the values the quantized bytes stand for.
   * torch.cuda: the handful of calls these programs make (streams, events, synchronize, memory
     statistics, device queries) as host stand-ins; `init_process_group('nccl')` becomes gloo.
-  * CUDA graphs: `torch.cuda.graph` records what runs inside it - every ATen operation (a
+  * CUDA graphs: during a capture, what a real capture refuses is refused here too (synchronizing
+    the device, a stream or an event; reading a tensor from the host with .item(), .tolist(), .cpu(),
+    bool() and the like). `torch.cuda.graph` records what runs inside it - every ATen operation (a
     torch-dispatch mode sees forward and backward alike) and every simulated kernel launch, each with
     the very tensors and raw arguments it ran on - and `CUDAGraph.replay()` runs the recording again
     in order, writing results into the recorded output tensors. Host decisions taken during capture
@@ -51,11 +53,23 @@ ROOT = os.path.dirname(HERE)
 STATE = types.SimpleNamespace(recording=None, cpu_is_elsewhere=False, program=None)
 
 
+def _not_while_capturing(what):
+    """A real capture fails on anything that waits for the device or reads device memory from the
+    host; the emulation refuses the same, outside the simulated launches (which are host code here)."""
+    recording = STATE.recording
+    if recording is not None and not recording.inside_launch and not recording.replaying:
+        raise RuntimeError(f'{what}: operation not permitted while a stream is capturing (emulated capture)')
+
+
 # ---------------------------------------------------------------------------------------- devices
 def _is_cuda(value):
     if isinstance(value, torch.device):
         return value.type == 'cuda'
     return isinstance(value, str) and value.startswith('cuda')
+
+
+HOST_READS = {torch.Tensor.item, torch.Tensor.tolist, torch.Tensor.numpy, torch.Tensor.__bool__, torch.Tensor.__int__,
+              torch.Tensor.__float__, torch.Tensor.__index__, torch.Tensor.cpu}
 
 
 class OnHost(TorchFunctionMode):
@@ -76,6 +90,8 @@ class OnHost(TorchFunctionMode):
             return args[0].to('meta')      # only where the program itself says .cpu(), not in libraries
         if getattr(func, '__self__', None) is torch.Tensor.is_cuda:   # the property's getter
             return args[0].device.type == 'cpu'
+        if func in HOST_READS and isinstance(args[0], torch.Tensor) and args[0].device.type == 'cpu':
+            _not_while_capturing(f'Tensor.{func.__name__}')
         if func is torch.Tensor.to:
             args = tuple('cpu' if _is_cuda(a) else a for a in args)
             kwargs.pop('non_blocking', None)
@@ -92,6 +108,7 @@ class Recording(TorchDispatchMode):
         super().__init__()
         self.nodes = []
         self.inside_launch = False
+        self.replaying = False
 
     def __torch_dispatch__(self, func, types_, args=(), kwargs=None):
         kwargs = kwargs or {}
@@ -188,7 +205,7 @@ class Stream:
         return None
 
     def synchronize(self):
-        return None
+        _not_while_capturing('Stream.synchronize')
 
     def query(self):
         return True
@@ -214,7 +231,7 @@ class Event:
         self.at = time.perf_counter()
 
     def synchronize(self):
-        return None
+        _not_while_capturing('Event.synchronize')
 
     def wait(self, stream=None):
         return None
@@ -245,7 +262,7 @@ def _properties(device=None):
 
 CUDA_STAND_INS = dict(
     is_available=lambda: True, device_count=lambda: 1, set_device=lambda device: None, current_device=lambda: 0,
-    synchronize=lambda device=None: None, Stream=Stream, Event=Event, stream=_stream_context,
+    synchronize=lambda device=None: _not_while_capturing('torch.cuda.synchronize'), Stream=Stream, Event=Event, stream=_stream_context,
     current_stream=_current_stream, default_stream=_current_stream, set_stream=lambda stream: None,
     CUDAGraph=Graph, graph=capture, is_current_stream_capturing=lambda: STATE.recording is not None,
     memory_allocated=lambda device=None: 0, max_memory_allocated=lambda device=None: 0,
@@ -315,7 +332,14 @@ def _varlen_attention(q, k, v, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_
                       causal=False, softmax_scale=None, **_):
     """Stand-in for a variable-length flash-attention call ([tokens, heads, dim] operands, sequences
     delimited by cu_seqlens): torch's math attention per sequence, FP32 inside, the operands' type out."""
-    bounds_q, bounds_k = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    recording = STATE.recording      # the real function takes the sequence bounds on the device; this one reads them
+    if recording is not None:
+        recording.inside_launch = True
+    try:
+        bounds_q, bounds_k = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    finally:
+        if recording is not None:
+            recording.inside_launch = False
     pieces = []
     for (q0, q1), (k0, k1) in zip(zip(bounds_q, bounds_q[1:]), zip(bounds_k, bounds_k[1:])):
         out = torch.nn.functional.scaled_dot_product_attention(
