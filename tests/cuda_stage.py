@@ -237,6 +237,7 @@ class Event:
         return None
 
     def query(self):
+        _not_while_capturing('Event.query')
         return True
 
     def elapsed_time(self, end):
