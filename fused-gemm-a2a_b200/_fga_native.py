@@ -57,6 +57,9 @@ def _declare(l):
     l.fga_gemm_push_mx.argtypes = [vp, vp, i64, i, i, vp, vp, i64, vp, i, i, pp, i64, i, i, vp, c_uint64, vp]
     l.fga_gemm_recv_mx.argtypes = [vp, vp, vp, i, i, vp, vp, i64, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i,
                                    vp, vp, vp, c_uint64, vp]
+    l.fga_gemm_push_gqa_mx.argtypes = [vp, vp, i64, i, i, vp, vp, i64, vp, i, i, i, pp, i64, i, i, vp, c_uint64, vp]
+    l.fga_gemm_recv_gqa_mx.argtypes = [vp, vp, vp, i, vp, vp, i64, i, i, vp, vp, vp, vp, pp, i, i, i, i, i, i, i, i,
+                                       vp, vp, c_uint64, vp]
     l.fga_copy_rank_rows.argtypes = [pp, pp, i, i, i64, i64, i, vp, i, i, vp]
     l.fga_bias_grad_scratch_floats.argtypes = [i64, i]
     l.fga_bias_grad_scratch_floats.restype = i64
@@ -68,7 +71,7 @@ def _declare(l):
                  'fga_symm_free', 'fga_symm_alloc_vmm', 'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push', 'fga_gemm_recv',
                  'fga_gemm_push_gqa', 'fga_gemm_recv_gqa',
                  'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
-                 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
+                 'fga_gemm_push_gqa_mx', 'fga_gemm_recv_gqa_mx', 'fga_copy_rank_rows', 'fga_bias_grad', 'fga_bias_grad_static',
                  'fga_mx_quantize'):
         getattr(l, name).restype = i
 
@@ -77,7 +80,7 @@ EXPORTS = ('fga_version', 'fga_last_error', 'fga_sm_count', 'fga_launch_count', 
            'fga_symm_open', 'fga_symm_close', 'fga_symm_free', 'fga_symm_vmm_size', 'fga_symm_alloc_vmm',
            'fga_symm_open_vmm', 'fga_symm_release_vmm', 'fga_barrier', 'fga_gemm_push',
            'fga_gemm_recv', 'fga_gemm_push_gqa', 'fga_gemm_recv_gqa', 'fga_gemm_local', 'fga_gemm_local_mx', 'fga_gemm_push_mx', 'fga_gemm_recv_mx',
-           'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
+           'fga_gemm_push_gqa_mx', 'fga_gemm_recv_gqa_mx', 'fga_copy_rank_rows', 'fga_bias_grad_scratch_floats',
            'fga_bias_grad', 'fga_bias_grad_static_capacity_floats', 'fga_bias_grad_static', 'fga_mx_quantize')
 
 

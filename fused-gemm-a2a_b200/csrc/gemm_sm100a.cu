@@ -559,4 +559,98 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
   return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
 }
 
+// ---- grouped-query attention with MXFP8 operands: the block-scaled launches above with the grouped
+// column layout of fga_gemm_push_gqa / fga_gemm_recv_gqa.
+
+int fga_gemm_push_gqa_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int kp, int a_rows, const void* bq,
+                         const void* sfb, int64_t b_rows_padded, const void* bias, int kv_heads, int q_per_kv,
+                         int gate, const int64_t* const* peer_heads, int64_t head_rows, int rank, int p,
+                         int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(aq && sfa && bq && sfb && peer_heads && status, "fga_gemm_push_gqa_mx: null argument");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_push_gqa_mx: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(kv_heads >= 1 && kv_heads % p == 0 && q_per_kv >= 1 && q_per_kv <= 64,
+              "Key/value heads must split evenly over CP ranks (kv_heads=%d, q_per_kv=%d, p=%d)", kv_heads,
+              q_per_kv, p);
+  FGA_REQUIRE(kp >= 128 && kp % 128 == 0, "fga_gemm_push_gqa_mx: padded K must be a multiple of 128");
+  FGA_REQUIRE(a_rows >= 256 && a_rows % 256 == 0 && a_rows <= a_rows_padded && a_rows <= head_rows,
+              "a_rows must be a tile multiple within the quantized rows and the head-side rank block");
+  const int kinds = gate ? 4 : 3;
+  for (int s = 0; s < kinds; ++s) FGA_REQUIRE(peer_heads[s], "fga_gemm_push_gqa_mx: null peer table %d", s);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(bias) % 16 == 0, "fga_gemm_push_gqa_mx: the bias must be 16-byte aligned");
+  const sched::HeadLayout layout = grouped_layout(kv_heads, q_per_kv, gate, p);
+  const long long units = static_cast<long long>(kv_heads) * sched::group_units(layout);
+  FGA_REQUIRE(units * 128 <= 2147483647LL, "fga_gemm_push_gqa_mx: too many output columns");
+  const int n = static_cast<int>(units) * 128;
+  FGA_REQUIRE(b_rows_padded >= n && b_rows_padded % 128 == 0, "fga_gemm_push_gqa_mx: weight rows must be padded");
+  GemmParams P{};
+  P.bn = mx_tile_n(units % 2 == 0 && b_rows_padded % 256 == 0);
+  P.acc_stages = P.bn == 256 ? 1 : 2;
+  P.m_tiles = a_rows / 256;
+  P.k_tiles = kp / 128;
+  P.idesc = make_idesc_mx(P.bn);
+  fill_push(P, n, layout, peer_heads, kinds, head_rows, rank, p, bias, status, timeout_ns);
+  P.sfa_kblocks = P.sfb_kblocks = kp / 128;
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = encode_mx_operand(&ta, &tsa, aq, sfa, a_rows_padded, kp, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, kp, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
+}
+
+int fga_gemm_recv_gqa_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_rows, const void* bq,
+                         const void* sfb, int64_t b_rows_padded, int b_kp, int n, void* c, const int64_t* peer_recv,
+                         const int64_t* peer_counters, int32_t* counters, const void* const* srcs, int kv_heads,
+                         int q_per_kv, int gate, int src_rows, int split, int rank, int p, int roles,
+                         int32_t* progress, int32_t* status, uint64_t timeout_ns, void* stream) {
+  FGA_REQUIRE(recv && mx_recv && mx_scale && bq && sfb && c && peer_recv && peer_counters && counters && srcs &&
+                  status,
+              "fga_gemm_recv_gqa_mx: null argument");
+  FGA_REQUIRE(p >= 1 && p <= 32 && rank >= 0 && rank < p, "fga_gemm_recv_gqa_mx: bad rank %d of %d", rank, p);
+  FGA_REQUIRE(kv_heads >= 1 && kv_heads % p == 0 && q_per_kv >= 1 && q_per_kv <= 64,
+              "Key/value heads must split evenly over CP ranks (kv_heads=%d, q_per_kv=%d, p=%d)", kv_heads,
+              q_per_kv, p);
+  FGA_REQUIRE(recv_rows >= 256 && recv_rows % 256 == 0,
+              "fga_gemm_recv_gqa_mx: receive rows must be a multiple of 256");
+  FGA_REQUIRE(src_rows >= 1 && src_rows <= recv_rows,
+              "Receive source rows must be positive and fit the receive buffer");
+  FGA_REQUIRE(split >= 1 && 128 % split == 0, "FUSED_PUSH_SPLIT must divide 128");
+  FGA_REQUIRE((roles & 3) != 0 && (roles & ~3) == 0,
+              "fga_gemm_recv_gqa_mx: roles is a mask of 1 (GEMM) and 2 (pushers)");
+  const int num_in = gate ? 4 : 3;
+  for (int t = 0; t < num_in; ++t)
+    FGA_REQUIRE(srcs[t] && reinterpret_cast<uintptr_t>(srcs[t]) % 16 == 0,
+                "fga_gemm_recv_gqa_mx: source %d must be a 16-byte aligned device pointer", t);
+  FGA_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "fga_gemm_recv_gqa_mx: output must be 16-byte aligned");
+  const sched::HeadLayout layout = grouped_layout(kv_heads, q_per_kv, gate, p);
+  const long long units = static_cast<long long>(kv_heads) * sched::group_units(layout);
+  FGA_REQUIRE(units * 128 <= 2147483647LL, "fga_gemm_recv_gqa_mx: receive rows too wide");
+  const int k = static_cast<int>(units) * 128;
+  FGA_REQUIRE(b_kp >= k && b_kp % 128 == 0, "fga_gemm_recv_gqa_mx: the weight's padded K must cover K");
+  FGA_REQUIRE(n >= 128 && n % 128 == 0 && b_rows_padded >= n && b_rows_padded % 128 == 0,
+              "GEMM mode must be push/recv and tile N must divide output width");
+  GemmParams P{};
+  P.bn = mx_tile_n(n % 256 == 0 && b_rows_padded % 256 == 0);
+  P.acc_stages = P.bn == 256 ? 1 : 2;
+  P.k_tiles = k / 128;
+  P.idesc = make_idesc_mx(P.bn);
+  fill_recv(P, recv_rows, k, n, c, layout, peer_recv, peer_counters, counters, srcs, num_in, src_rows, split, rank,
+            p, roles, status, timeout_ns);
+  P.quant_arrivals = p * num_in * split;
+  P.target = P.quant_arrivals + 16;
+  int rc = pace_pushers(P, progress, static_cast<cudaStream_t>(stream));
+  if (rc != kSuccess) return rc;
+  P.quant_src = static_cast<const uint16_t*>(recv);
+  P.quant_q = static_cast<uint8_t*>(mx_recv);
+  P.quant_sf = static_cast<uint8_t*>(mx_scale);
+  P.sfa_kblocks = k / 128;
+  P.sfb_kblocks = b_kp / 128;
+  CUtensorMap ta, tb, tsa, tsb;
+  rc = encode_mx_operand(&ta, &tsa, mx_recv, mx_scale, recv_rows, k, 128);
+  if (rc != kSuccess) return rc;
+  rc = encode_mx_operand(&tb, &tsb, bq, sfb, b_rows_padded, b_kp, P.bn / 2);
+  if (rc != kSuccess) return rc;
+  return launch(ta, tb, P, static_cast<cudaStream_t>(stream), &tsa, &tsb);
+}
+
 }  // extern "C"

@@ -686,35 +686,58 @@ class _Comm:
             counters.data_ptr(), sources, num_in, src_rows, split, self.rank, self.p, roles,
             self._pacing_epoch(), self.progress.data_ptr(), self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
 
-    def push_gqa(self, a, a_rows, weight, bias, peer_tables, layout, head_rows):
+    def push_gqa(self, a, a_rows, weight, bias, peer_tables, layout, head_rows, scales=()):
         """QKV forward with more query heads than key/value heads: `weight` rows (and `bias`) are grouped
         per key/value head, layout = (kv_heads, q_per_kv, gate); one head-side buffer per kind
-        (q, k, v(, gate)), the k and v buffers 1/q_per_kv as wide as the q buffer."""
+        (q, k, v(, gate)), the k and v buffers 1/q_per_kv as wide as the q buffer. With `scales` both
+        operands are what mxfp8_quantize made of them (E4M3 payload, padded) and scales = (sa, sb)."""
         kv_heads, q_per_kv, gate = layout
         if not (a.is_contiguous() and weight.is_contiguous()):
             raise ValueError('Fused kernels need contiguous tensors')
         if len(peer_tables) != (4 if gate else 3) or not all(len(table) == self.p for table in peer_tables):
             raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
         tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
+        stream = torch.cuda.current_stream().cuda_stream
+        bias_address = bias.data_ptr() if bias is not None else 0
+        if scales:
+            sa, sb = scales
+            _native.check(_native.lib().fga_gemm_push_gqa_mx(
+                a.data_ptr(), sa.data_ptr(), a.shape[0], a.shape[1], a_rows, weight.data_ptr(), sb.data_ptr(),
+                weight.shape[0], bias_address, kv_heads, q_per_kv, int(gate), tables, head_rows, self.rank, self.p,
+                self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
+            return
         _native.check(_native.lib().fga_gemm_push_gqa(
-            a.data_ptr(), a.shape[0], a.shape[1], a_rows, weight.data_ptr(), bias.data_ptr() if bias is not None else 0,
+            a.data_ptr(), a.shape[0], a.shape[1], a_rows, weight.data_ptr(), bias_address,
             kv_heads, q_per_kv, int(gate), tables, head_rows, self.rank, self.p, self.status.data_ptr(),
-            _k.DEVICE_TIMEOUT_NS, torch.cuda.current_stream().cuda_stream))
+            _k.DEVICE_TIMEOUT_NS, stream))
 
-    def recv_gqa(self, recv, weight, out, peer_recv, peer_counters, counters, inputs, src_rows, layout, roles=3):
+    def recv_gqa(self, recv, weight, out, peer_recv, peer_counters, counters, inputs, src_rows, layout, roles=3,
+                 scales=(), mx=None):
         """QKV dgrad for the same layout: `inputs` are the head-side gradients of q, k, v(, gate), whose
-        rows are of different widths; `weight` is [rows of the grouped layout, H]."""
+        rows are of different widths; `weight` is [rows of the grouped layout, H]. With `scales` = (sb,)
+        the weight is its quantized transpose [pad(H), pad(K)] and mx = (local E4M3 copy of the receive
+        buffer, its scale bytes), which the kernel's quantizer warps fill."""
         kv_heads, q_per_kv, gate = layout
         if counters.numel() != out.shape[0] // CTA_M or recv.shape[0] != out.shape[0]:
             raise ValueError('Peer pointer arrays must have P entries and counters one per row block')
-        hidden = weight.shape[1]
+        hidden = out.shape[1]
         split = push_split(len(inputs) * hidden, self.p, len(inputs), PUSH_SPLIT)   # sized by the widest input
         sources = _native.ptr_array([t.data_ptr() for t in inputs])
+        stream = torch.cuda.current_stream().cuda_stream
+        if scales:
+            mx_recv, mx_scale = mx
+            _native.check(_native.lib().fga_gemm_recv_gqa_mx(
+                recv.data_ptr(), mx_recv.data_ptr(), mx_scale.data_ptr(), recv.shape[0], weight.data_ptr(),
+                scales[-1].data_ptr(), weight.shape[0], weight.shape[1], out.shape[1], out.data_ptr(),
+                peer_recv.data_ptr(), peer_counters.data_ptr(), counters.data_ptr(), sources, kv_heads, q_per_kv,
+                int(gate), src_rows, split, self.rank, self.p, roles, self.progress.data_ptr(),
+                self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS, stream))
+            return
         _native.check(_native.lib().fga_gemm_recv_gqa(
             recv.data_ptr(), recv.shape[0], weight.data_ptr(), out.shape[1], out.data_ptr(), peer_recv.data_ptr(),
             peer_counters.data_ptr(), counters.data_ptr(), sources, kv_heads, q_per_kv, int(gate), src_rows, split,
             self.rank, self.p, roles, self.progress.data_ptr(), self.status.data_ptr(), _k.DEVICE_TIMEOUT_NS,
-            torch.cuda.current_stream().cuda_stream))
+            stream))
 
     def _launch_push(self, a, a_rows, b, b_is_kn, bias, peer_tables, n_segment, head_rows):
         tables = _native.ptr_array([table.data_ptr() for table in peer_tables])
@@ -1016,6 +1039,11 @@ class _ProjectionWorkspace:
         if self.layout is not None and segments > 1:
             if b_is_kn:
                 raise ValueError('The grouped-query push takes the weight as [rows, K]')
+            if self.precision == 'mxfp8':
+                aq, sa = mxfp8_quantize(a)
+                wq, sb = _quantized_weight(weight, False)
+                comm.push_gqa(aq, self.capacity, wq, bias, self.peer_heads, self.layout, self.capacity, scales=(sa, sb))
+                return
             comm.push_gqa(a, self.capacity, weight, bias, self.peer_heads, self.layout, self.capacity)
             return
         width = weight.shape[1] if b_is_kn else weight.shape[0]
@@ -1047,6 +1075,11 @@ class _ProjectionWorkspace:
         if grouped:
             if not b_is_kn:
                 raise ValueError('The grouped-query dgrad takes the weight as [K, N]')
+            if self.precision == 'mxfp8':
+                wq, sb = _quantized_weight(weight, True)
+                comm.recv_gqa(self.recv, wq, out, self.peer_recv, self.peer_counters, self.counters, inputs, src_rows,
+                              self.layout, roles=roles, scales=(sb,), mx=(self.mx_recv, self.mx_scale))
+                return
             comm.recv_gqa(self.recv, weight, out, self.peer_recv, self.peer_counters, self.counters, inputs, src_rows,
                           self.layout, roles=roles)
             return
@@ -1117,8 +1150,6 @@ class FusedGemmA2AWorkspace:
         if kv_heads != self.num_heads:
             if kv_heads < 1 or self.num_heads % kv_heads or kv_heads % peers:
                 raise ValueError('Query heads must be a multiple of key/value heads, which must split over CP')
-            if quantized:
-                raise NotImplementedError('MXFP8 with grouped-query attention is not supported yet')
         comm = _Comm.get(group)
         # One buffer set for the QKV(/gate) side and one for the output side, shared by every
         # workspace handle and layer of the same geometry on this group.

@@ -194,6 +194,19 @@ int fga_gemm_recv_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_r
                      int roles, const int64_t* epoch, int32_t* progress, int32_t* status,
                      uint64_t timeout_ns, void* stream);
 
+/* Grouped-query attention with MXFP8 operands: fga_gemm_push_mx / fga_gemm_recv_mx with the grouped
+ * column layout of fga_gemm_push_gqa / fga_gemm_recv_gqa (same buffers, tables and source widths). No
+ * counterpart in the reference, whose fused modules reject these shapes. */
+int fga_gemm_push_gqa_mx(const void* aq, const void* sfa, int64_t a_rows_padded, int kp, int a_rows, const void* bq,
+                         const void* sfb, int64_t b_rows_padded, const void* bias, int kv_heads, int q_per_kv,
+                         int gate, const int64_t* const* peer_heads, int64_t head_rows, int rank, int p,
+                         int32_t* status, uint64_t timeout_ns, void* stream);
+int fga_gemm_recv_gqa_mx(const void* recv, void* mx_recv, void* mx_scale, int recv_rows, const void* bq,
+                         const void* sfb, int64_t b_rows_padded, int b_kp, int n, void* c, const int64_t* peer_recv,
+                         const int64_t* peer_counters, int32_t* counters, const void* const* srcs, int kv_heads,
+                         int q_per_kv, int gate, int src_rows, int split, int rank, int p, int roles,
+                         int32_t* progress, int32_t* status, uint64_t timeout_ns, void* stream);
+
 /* ---- auxiliary kernels -------------------------------------------------------------------- */
 
 /* Replaces resize_rank_rows (fused_gemm_a2a_kernels.py:1145-1188). in/out: `segments` BF16

@@ -337,19 +337,9 @@ class SimulatedLibrary:
         """(first unit, units) of q, k, v(, gate) inside one key/value group."""
         return [(0, q_per_kv), (q_per_kv, 1), (q_per_kv + 1, 1)] + ([(q_per_kv + 2, q_per_kv)] if gate else [])
 
-    @_as_launch
-    def fga_gemm_push_gqa(self, a, m, k, a_rows, b, bias, kv_heads, q_per_kv, gate, tables, head_rows, rank, p,
-                          status, timeout, stream):
-        self.launches += 1
+    def _route_push_gqa(self, product, a_rows, kv_heads, q_per_kv, gate, tables, head_rows, rank, p):
         kinds = self._kinds(q_per_kv, gate)
         per_group, groups = kinds[-1][0] + kinds[-1][1], kv_heads // p
-        n = kv_heads * per_group * 128
-        padded = torch.zeros(a_rows, k, dtype=BF16)
-        padded[:m] = matrix(a, m, k)
-        product = padded.float() @ matrix(b, n, k).float().t()
-        if bias:
-            product = product + matrix(bias, 1, n).float()
-        product = product.to(BF16)
         for unit in range(kv_heads * per_group):
             group, position = divmod(unit, per_group)
             kind = max(index for index, (first, _) in enumerate(kinds) if position >= first)
@@ -358,12 +348,39 @@ class SimulatedLibrary:
             column = (local * units + position - first) * 128
             target = matrix(table(tables[kind], p)[dest], p * head_rows, groups * units * 128)
             target[rank * head_rows:rank * head_rows + a_rows, column:column + 128] = product[:, unit * 128:(unit + 1) * 128]
+
+    @_as_launch
+    def fga_gemm_push_gqa(self, a, m, k, a_rows, b, bias, kv_heads, q_per_kv, gate, tables, head_rows, rank, p,
+                          status, timeout, stream):
+        self.launches += 1
+        kinds = self._kinds(q_per_kv, gate)
+        n = kv_heads * (kinds[-1][0] + kinds[-1][1]) * 128
+        padded = torch.zeros(a_rows, k, dtype=BF16)
+        padded[:m] = matrix(a, m, k)
+        product = padded.float() @ matrix(b, n, k).float().t()
+        if bias:
+            product = product + matrix(bias, 1, n).float()
+        self._route_push_gqa(product.to(BF16), a_rows, kv_heads, q_per_kv, gate, tables, head_rows, rank, p)
         return 0
 
     @_as_launch
-    def fga_gemm_recv_gqa(self, recv, recv_rows, b, n, c, peer_recv, peer_counters, counters, srcs, kv_heads, q_per_kv,
-                          gate, src_rows, split, rank, p, roles, progress, status, timeout, stream):
+    def fga_gemm_push_gqa_mx(self, aq, sfa, a_rows_padded, kp, a_rows, bq, sfb, b_rows_padded, bias, kv_heads, q_per_kv,
+                             gate, tables, head_rows, rank, p, status, timeout, stream):
         self.launches += 1
+        kinds = self._kinds(q_per_kv, gate)
+        n = kv_heads * (kinds[-1][0] + kinds[-1][1]) * 128
+        activations, weight = self.source_of(aq), self.source_of(bq)     # [m, k] and [n, k]
+        assert weight.shape[0] == n and activations.shape[1] == weight.shape[1]
+        assert a_rows_padded >= a_rows >= activations.shape[0] and b_rows_padded >= n and kp >= weight.shape[1]
+        product = torch.zeros(a_rows, n)
+        product[:activations.shape[0]] = mx_product(activations, weight)
+        if bias:
+            product = product + matrix(bias, 1, n).float()
+        self._route_push_gqa(product.to(BF16), a_rows, kv_heads, q_per_kv, gate, tables, head_rows, rank, p)
+        return 0
+
+    def _push_inputs_gqa(self, recv_rows, peer_recv, peer_counters, srcs, kv_heads, q_per_kv, gate, src_rows, split,
+                         rank, p, roles):
         kinds = self._kinds(q_per_kv, gate)
         per_group, groups = kinds[-1][0] + kinds[-1][1], kv_heads // p
         k = kv_heads * per_group * 128
@@ -387,10 +404,48 @@ class SimulatedLibrary:
             _meet()
         if not roles & 2:
             _meet()
+        return k, len(kinds)
+
+    @_as_launch
+    def fga_gemm_recv_gqa(self, recv, recv_rows, b, n, c, peer_recv, peer_counters, counters, srcs, kv_heads, q_per_kv,
+                          gate, src_rows, split, rank, p, roles, progress, status, timeout, stream):
+        self.launches += 1
+        k, num_in = self._push_inputs_gqa(recv_rows, peer_recv, peer_counters, srcs, kv_heads, q_per_kv, gate, src_rows,
+                                          split, rank, p, roles)
         if roles & 1:
-            if not self._arrived(counters, recv_rows, p * len(kinds) * split, roles):
+            if not self._arrived(counters, recv_rows, p * num_in * split, roles):
                 return -2
             matrix(c, recv_rows, n)[:] = (matrix(recv, recv_rows, k).float() @ matrix(b, k, n).float()).to(BF16)
+        return 0
+
+    def _quantize_received(self, recv, mx_recv, mx_scale, counters, recv_rows, k):
+        """What the quantizer warps leave behind: the E4M3 copy of the receive buffer and its scales (K
+        padded to 128), and their 16 completions per row block on the arrival counters."""
+        from oracle import mxfp8_oracle
+        received = matrix(recv, recv_rows, k)
+        payload, scales = mxfp8_oracle.quantize(bf16_bits(received), k_multiple=128)
+        torch.frombuffer(_bytes_at(mx_recv, recv_rows * k), dtype=torch.uint8).copy_(
+            torch.from_numpy(payload[:recv_rows, :k].copy()).reshape(-1))
+        torch.frombuffer(_bytes_at(mx_scale, recv_rows * k // 32), dtype=torch.uint8).copy_(
+            torch.from_numpy(scales[:recv_rows * k // 32].copy()))
+        own = torch.frombuffer(_bytes_at(counters, 4 * (recv_rows // 128)), dtype=torch.int32)
+        own += 16
+        return received
+
+    @_as_launch
+    def fga_gemm_recv_gqa_mx(self, recv, mx_recv, mx_scale, recv_rows, bq, sfb, b_rows_padded, b_kp, n, c, peer_recv,
+                             peer_counters, counters, srcs, kv_heads, q_per_kv, gate, src_rows, split, rank, p, roles,
+                             progress, status, timeout, stream):
+        self.launches += 1
+        k, num_in = self._push_inputs_gqa(recv_rows, peer_recv, peer_counters, srcs, kv_heads, q_per_kv, gate, src_rows,
+                                          split, rank, p, roles)
+        if roles & 1:
+            if not self._arrived(counters, recv_rows, p * num_in * split, roles):
+                return -2
+            received = self._quantize_received(recv, mx_recv, mx_scale, counters, recv_rows, k)
+            weight = self.source_of(bq)
+            assert weight.shape == (n, k) and b_rows_padded >= n and b_kp >= k
+            matrix(c, recv_rows, n)[:] = mx_product(received, weight).to(BF16)
         return 0
 
     @_as_launch

@@ -56,6 +56,23 @@ CASES = [
      'Receive source rows'),
     (('fga_gemm_recv_gqa', (P, 512, P, 512, P + 8, P, P, P, TABLES, 8, 2, 1, 300, 2, 0, 4, 3, None, P, NS, None)),
      'output must be 16-byte aligned'),
+    # push_gqa_mx: aq, sfa, a_rows_padded, kp, a_rows, bq, sfb, b_rows_padded, bias, kv_heads, q_per_kv, gate, tables, ...
+    (('fga_gemm_push_gqa_mx', (P, P, 512, 512, 512, P, P, 4096, None, 6, 4, 0, TABLES, 512, 0, 4, P, NS, None)),
+     'split evenly over CP'),
+    (('fga_gemm_push_gqa_mx', (P, P, 512, 100, 512, P, P, 4096, None, 8, 2, 0, TABLES, 512, 0, 4, P, NS, None)),
+     'multiple of 128'),
+    (('fga_gemm_push_gqa_mx', (P, P, 512, 512, 300, P, P, 4096, None, 8, 2, 0, TABLES, 512, 0, 4, P, NS, None)),
+     'tile multiple'),
+    (('fga_gemm_push_gqa_mx', (P, P, 512, 512, 512, P, P, 1024, None, 8, 2, 0, TABLES, 512, 0, 4, P, NS, None)),
+     'weight rows must be padded'),
+    # recv_gqa_mx: recv, mx_recv, mx_scale, recv_rows, bq, sfb, b_rows_padded, b_kp, n, c, peer_recv, peer_counters,
+    #              counters, srcs, kv_heads, q_per_kv, gate, src_rows, split, rank, p, roles, progress, status, ...
+    (('fga_gemm_recv_gqa_mx', (P, P, P, 512, P, P, 512, 4096, 512, P, P, P, P, TABLES, 6, 2, 0, 300, 2, 0, 4, 3, None,
+                               P, NS, None)), 'split evenly over CP'),
+    (('fga_gemm_recv_gqa_mx', (P, P, P, 512, P, P, 512, 1024, 512, P, P, P, P, TABLES, 8, 2, 0, 300, 2, 0, 4, 3, None,
+                               P, NS, None)), "padded K must cover K"),
+    (('fga_gemm_recv_gqa_mx', (P, P, P, 512, P, P, 512, 4096, 512, P, P, P, P, TABLES, 8, 2, 0, 300, 2, 0, 4, 0, None,
+                               P, NS, None)), 'roles'),
     (recv(num_in=2), 'three/four'),
     (recv(recv_rows=300), 'multiple of 256'),
     (recv(src_rows=0), 'Receive source rows'),

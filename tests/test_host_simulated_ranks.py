@@ -464,7 +464,7 @@ def test_workspaces_on_cp_subgroups_before_posted_pipeline_receives():
         assert problems == [], f'rank {rank}: {problems}'
 
 
-def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, bias_in_gemm):
+def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, bias_in_gemm, precision='bf16'):
     """The public modules with fewer key/value heads than query heads, on simulated ranks, against the
     grouped-query oracle (itself pinned by the reference's unfused modules with num_kv_heads <
     num_heads): outputs of different widths per kind, transport buffers bit for bit, dX, parameter
@@ -477,7 +477,11 @@ def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, 
     torch.set_num_threads(2)
     import abi_simulator
     import fused_gemm_a2a as fused
+    from oracle import mxfp8_oracle, ulysses_oracle
     from oracle.ulysses_oracle import GroupedQueryOracle
+    quantized = precision == 'mxfp8'
+    if quantized:       # every GEMM of the oracle with both operands quantized along the reduction axis
+        ulysses_oracle._mm = lambda a, b, acc_dtype: abi_simulator.mx_product(a.to(BF), b.t().to(BF)).to(acc_dtype)
     p, d = world, 128
     hidden = heads * d
     r = heads // kv_heads
@@ -493,14 +497,14 @@ def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, 
         bq = torch.randn(rows, generator=g).mul(0.5).to(BF) if bias else None
         wq_p, wo_p = wq.clone().requires_grad_(), wo.clone().requires_grad_()
         bq_p = bq.clone().requires_grad_() if bias else None
-        ws = fused.FusedGemmA2AWorkspace(hidden, heads, 300, gate=gate, num_kv_heads=kv_heads)
+        ws = fused.FusedGemmA2AWorkspace(hidden, heads, 300, gate=gate, num_kv_heads=kv_heads, precision=precision)
         qkv = fused.FusedQKVProjection(hidden, heads, kv_heads, weight=wq_p, bias=bq_p, gate=gate,
                                        bias_in_gemm=bias_in_gemm)
         proj = fused.FusedOutputProjection(hidden, heads, weight=wo_p)
         oracle = GroupedQueryOracle(p, hidden, heads, kv_heads, gate, weight_qkv=wq, bias_qkv=bq, weight_out=wo,
                                     bias_in_gemm=bias_in_gemm)
         widths = [heads // p if kind in (0, 3) else kv_heads // p for kind in range(kinds)]
-        for tokens in (129, 300):
+        for tokens in ((129,) if quantized else (129, 300)):      # the numpy MXFP8 oracle is the slow side
             g = torch.Generator().manual_seed(1000 * tokens + rank)
             x = torch.randn(tokens, hidden, generator=g).to(BF).requires_grad_()
             grads = [torch.randn(p * tokens, width, d, generator=g).to(BF) for width in widths]
@@ -518,7 +522,12 @@ def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, 
             got = torch.autograd.grad(outs, [x, wq_p] + ([bq_p] if bias else []), grads)
             all_grads = everyone(tuple(grads))
             same(view.recv, oracle.qkv_recv_buffer(all_grads, rank, view.capacity), f'dY transport tokens={tokens}')
-            assert view.counters.tolist() == [p * kinds * fused.push_split(kinds * hidden, p, kinds)] * (view.capacity // 128)
+            arrivals = p * kinds * fused.push_split(kinds * hidden, p, kinds)
+            assert view.counters.tolist() == [arrivals + (16 if quantized else 0)] * (view.capacity // 128)
+            if quantized:     # the receive-side quantizer's copy is the standalone quantizer's output
+                payload, scales = mxfp8_oracle.quantize(abi_simulator.bf16_bits(view.recv), k_multiple=128)
+                assert torch.equal(view.mx_recv.view(torch.uint8), torch.from_numpy(payload[:view.capacity]))
+                assert torch.equal(view.mx_scale, torch.from_numpy(scales[:view.mx_scale.numel()]))
             rdx, rdw, rdb = oracle.qkv_backward(xs, all_grads)[rank]
             close(got[0], rdx, 'dx')
             close(got[1], rdw, 'dW_qkv (grouped row order)')
@@ -542,13 +551,15 @@ def grouped_query_worker(rank, world, port, queue, heads, kv_heads, gate, bias, 
         os._exit(1)
 
 
-@pytest.mark.parametrize('world,heads,kv_heads,gate,bias,bias_in_gemm', [
-    (1, 4, 2, False, False, False), (2, 8, 2, True, True, False), (2, 4, 2, False, True, True), (2, 6, 2, False, False, False)])
-def test_grouped_query_modules_on_simulated_ranks(world, heads, kv_heads, gate, bias, bias_in_gemm):
+@pytest.mark.parametrize('world,heads,kv_heads,gate,bias,bias_in_gemm,precision', [
+    (1, 4, 2, False, False, False, 'bf16'), (2, 8, 2, True, True, False, 'bf16'), (2, 4, 2, False, True, True, 'bf16'),
+    (2, 6, 2, False, False, False, 'bf16'), (2, 4, 2, True, True, False, 'mxfp8')])
+def test_grouped_query_modules_on_simulated_ranks(world, heads, kv_heads, gate, bias, bias_in_gemm, precision):
     ctx = mp.get_context('spawn')
     queue = ctx.Queue()
+    port = 29640 + heads + world + (20 if precision == 'mxfp8' else 0)
     procs = [ctx.Process(target=grouped_query_worker,
-                         args=(r, world, 29640 + heads + world, queue, heads, kv_heads, gate, bias, bias_in_gemm))
+                         args=(r, world, port, queue, heads, kv_heads, gate, bias, bias_in_gemm, precision))
              for r in range(world)]
     for proc in procs:
         proc.start()

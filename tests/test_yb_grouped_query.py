@@ -1,5 +1,5 @@
 """GPU parity of grouped-query attention (fewer key/value heads than query heads), an addition over
-the reference's fused modules, which reject it; expected values come from the grouped-query oracle,
+the reference's fused modules, which reject it (BF16 and MXFP8); expected values come from the grouped-query oracle,
 pinned by the reference's unfused modules run with num_kv_heads < num_heads
 (tests/test_oracle_golden.py).
 
@@ -154,3 +154,65 @@ def test_modules_match_the_grouped_query_oracle(cp1, heads, kv_heads, gate, with
     with pytest.raises(ValueError, match='QKV/QKVG mode'):
         FusedQKVProjection(hidden, heads, weight=torch.nn.Parameter(torch.empty(3 * hidden, hidden, dtype=BF, device=DEV)))(
             x_d.detach(), ws)
+
+
+# ---- MXFP8 operands with the grouped layout ------------------------------------------------------
+def _mx_mm(a, b, acc_dtype):
+    """The oracle's GEMM a @ b with both operands quantized to MXFP8 along the reduction axis and the
+    exact dequantized values multiplied (oracle/mxfp8_oracle.py)."""
+    import numpy as np
+    from oracle import mxfp8_oracle as mx
+
+    def bits(t):
+        return t.to(BF).contiguous().view(torch.int16).numpy().view(np.uint16)
+    return torch.from_numpy(mx.mx_matmul(bits(a), bits(b.t()))).to(acc_dtype)
+
+
+@pytest.mark.parametrize('heads,kv_heads,gate,with_bias,tokens', [(4, 2, False, False, 300), (8, 2, True, True, 129)])
+def test_mxfp8_modules_match_the_grouped_query_oracle(cp1, monkeypatch, heads, kv_heads, gate, with_bias, tokens):
+    """precision='mxfp8' with fewer key/value heads: the grouped push and receive launches with
+    block-scaled operands; the receive-side quantizer's bytes equal the standalone quantizer's."""
+    from fused_gemm_a2a import FusedGemmA2AWorkspace, FusedOutputProjection, FusedQKVProjection
+    from fused_gemm_a2a_kernels import mxfp8_quantize
+    from oracle import ulysses_oracle
+    monkeypatch.setattr(ulysses_oracle, '_mm', _mx_mm)
+    hidden = heads * 128
+    kinds, rows, widths = geometry(heads, kv_heads, gate, 1)
+    g = torch.Generator().manual_seed(tokens + heads)
+    wq = (torch.randn(rows, hidden, generator=g) / hidden ** 0.5).to(BF)
+    wo = (torch.randn(hidden, hidden, generator=g) / hidden ** 0.5).to(BF)
+    bq = torch.randn(rows, generator=g).mul(0.5).to(BF) if with_bias else None
+    x = torch.randn(tokens, hidden, generator=g).to(BF)
+    grads = tuple(torch.randn(tokens, widths[kind] // 128, 128, generator=g).to(BF) for kind in range(kinds))
+    o = torch.randn(tokens, heads, 128, generator=g).to(BF)
+    dy = torch.randn(tokens, hidden, generator=g).to(BF)
+    ws = FusedGemmA2AWorkspace(hidden, heads, 512, gate=gate, num_kv_heads=kv_heads, precision='mxfp8')
+    wq_p, wo_p = torch.nn.Parameter(wq.to(DEV)), torch.nn.Parameter(wo.to(DEV))
+    bq_p = torch.nn.Parameter(bq.to(DEV)) if with_bias else None
+    qkv = FusedQKVProjection(hidden, heads, kv_heads, weight=wq_p, bias=bq_p, gate=gate)
+    proj = FusedOutputProjection(hidden, heads, weight=wo_p)
+    x_d = x.to(DEV).requires_grad_()
+    outs = qkv(x_d, ws)
+    torch.autograd.backward(list(outs), [t.to(DEV) for t in grads])
+    view = ws._view(tokens, kinds)
+    q_ref, sf_ref = mxfp8_quantize(view.recv, k_multiple=128)
+    torch.cuda.synchronize()
+    assert torch.equal(view.mx_recv.view(torch.uint8), q_ref.view(torch.uint8)[:view.capacity])
+    assert torch.equal(view.mx_scale, sf_ref[:view.mx_scale.numel()])
+    o_d = o.to(DEV).requires_grad_()
+    y = proj(o_d, ws)
+    y.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    ws.comm.check_status()
+    oracle = GroupedQueryOracle(1, hidden, heads, kv_heads, gate, weight_qkv=wq, bias_qkv=bq, weight_out=wo)
+    for name, got, want in zip('qkvg', outs, oracle.qkv_forward([x])[0]):
+        close(got, want, name)
+    dx, dwq, dbq = oracle.qkv_backward([x], [grads])[0]
+    close(x_d.grad, dx, 'dx')
+    close(wq_p.grad, dwq, 'dW_qkv')
+    if with_bias:
+        close(bq_p.grad, dbq, 'dbias_qkv')
+    close(y, oracle.out_forward([o])[0], 'y')
+    dos, ((dwo, _),) = oracle.out_backward([o], [dy])
+    close(o_d.grad, dos[0], 'dO')
+    close(wo_p.grad, dwo, 'dW_o')
