@@ -8,7 +8,7 @@ names, arguments, error messages, caching, "no allocation after set-up", ownersh
 behaviour under graph replay with changed inputs - is exercised before a GPU ever sees it. Nothing
 here says anything about the kernels.
 
-    python tests/cuda_stage.py [--ranks N] [--port P] [--cpu-is-elsewhere] [--stand-in-attention]
+    python tests/cuda_stage.py [--ranks N] [--port P] [--cpu-is-elsewhere] [--stand-in-attention] [--real-library]
                                (<script.py> | -m <module>) [arguments...]
 
 One process per rank: with --ranks N this file starts N copies of itself with RANK / LOCAL_RANK /
@@ -21,6 +21,8 @@ provides:
     With --stand-in-attention the flash-attention function one test program imports is torch's math
     attention. torch's block-scaled matmul, which the reference's MXFP8 checks multiply with, is an
     exact product of the values the quantized bytes stand for.
+  * --real-library keeps libfga.so itself instead of the simulated library: whatever it answers before it
+    touches a device - its argument validation - then works in a process without a GPU.
   * torch.cuda: the handful of calls these programs make (streams, events, synchronize, memory
     statistics, device queries) as host stand-ins; `init_process_group('nccl')` becomes gloo.
   * CUDA graphs: during a capture, what a real capture refuses is refused here too (synchronizing
@@ -308,7 +310,7 @@ def _init_process_group(original):
     return init
 
 
-def install(cpu_is_elsewhere=False):
+def install(cpu_is_elsewhere=False, real_library=False):
     """Patch this process; returns nothing - the process is the stage's for the rest of its life."""
     for path in (os.path.join(ROOT, 'fused-gemm-a2a_b200'), HERE, ROOT):
         if path not in sys.path:
@@ -320,6 +322,12 @@ def install(cpu_is_elsewhere=False):
         setattr(torch.cuda, name, stand_in)
     dist.init_process_group = _init_process_group(dist.init_process_group)
     torch.Generator = _HostGenerator
+    if real_library:
+        # libfga.so itself: only what it answers before it touches a device can work here, i.e. its
+        # argument validation (tests that expect a rejection and its message).
+        fused.torch = _PackageTorch()
+        OnHost().__enter__()
+        return None
     _, undo = abi_simulator.install(fused, abi_simulator.unique_tag())
     # The package's own view of torch: the CPU is "the device" (its index is None), and every torch.cuda
     # call goes to the stand-ins above through the real module, so that a program which patches
@@ -411,7 +419,7 @@ def main():
     flags = []
     while arguments and arguments[0].startswith('--'):   # the stage's own options come first
         flag = arguments.pop(0)
-        if flag in ('--cpu-is-elsewhere', '--stand-in-attention'):
+        if flag in ('--cpu-is-elsewhere', '--stand-in-attention', '--real-library'):
             flags.append(flag)
         elif flag[2:] in options:
             options[flag[2:]] = int(arguments.pop(0))
@@ -427,7 +435,7 @@ def main():
         os.environ.setdefault(name, value)
     threads = int(os.environ.get('FGA_STAGE_THREADS', 0)) or (os.cpu_count() or 2) // int(os.environ['WORLD_SIZE'])
     torch.set_num_threads(max(1, threads))
-    install('--cpu-is-elsewhere' in flags)
+    install('--cpu-is-elsewhere' in flags, '--real-library' in flags)
     if '--stand-in-attention' in flags:
         _stand_in_attention()
     _stand_in_scaled_mm()

@@ -187,7 +187,7 @@ def test_argument_validation(cp1):
         qkv(probe[:1].cpu(), ws)
     with pytest.raises(ValueError, match='one N tile per head'):
         FusedQKVProjection(hidden, heads // 2, weight=w)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match='shape'):     # fewer key/value heads: the weight has fewer rows
         FusedQKVProjection(hidden, heads, heads // 2, weight=w)
     gated = FusedQKVProjection(hidden, heads, weight=torch.empty(4 * hidden, hidden, dtype=torch.bfloat16, device=DEV), gate=True)
     with pytest.raises(ValueError, match='QKV/QKVG mode'):
