@@ -333,8 +333,27 @@ def install(cpu_is_elsewhere=False, real_library=False):
     # call goes to the stand-ins above through the real module, so that a program which patches
     # torch.cuda.synchronize to catch a forbidden call also catches the package's.
     fused.torch = _PackageTorch()
+    _sabotage(fused, os.environ.get('FGA_STAGE_SABOTAGE', ''))
     OnHost().__enter__()
     return undo
+
+
+def _sabotage(fused, what):
+    """Negative controls: break the host layer in a known way, so that a test can show that the staged
+    programs notice (tests/test_reference_programs_staged.py).
+      shared-output   results that need no resizing are handed out as views of the shared head-side
+                      buffers instead of owned copies (the next forward overwrites them)"""
+    if what == 'shared-output':
+        owned = fused.resize_rank_rows
+
+        def resize_rank_rows(tensors, peers, rows, *, copy=False, bias=None, **kwargs):
+            tensors = tuple(tensors)
+            if bias is None and tensors[0].shape[0] == peers * rows:
+                return tensors
+            return owned(tensors, peers, rows, copy=copy, bias=bias, **kwargs)
+        fused.resize_rank_rows = resize_rank_rows
+    elif what:
+        raise SystemExit(f'unknown sabotage {what!r}')
 
 
 def _varlen_attention(q, k, v, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None,

@@ -143,3 +143,18 @@ def test_reference_program_passes_on_the_cpu_stage(running, name):
         if name == 'bench_fused':
             assert line['e2e']['h2d_bytes_per_step'] > 0 and line['e2e']['d2h_bytes_per_step'] > 0
             assert line['cpu_baseline']['kind'] == 'reference' and line['roofline']['launches_timed'] > 0
+
+
+def test_a_staged_program_notices_a_host_layer_without_ownership_copies(tmp_path):
+    """Negative control: with results handed out as views of the shared head-side buffers
+    (FGA_STAGE_SABOTAGE=shared-output breaks the package that way inside the stage), the reference's
+    training driver must fail on its own ownership assertion - the staged programs are not passing by
+    default."""
+    result = subprocess.run(
+        [sys.executable, STAGE, '--port', '29760', '--stand-in-attention',
+         os.path.join(STAGED, 'tests', 'attention_training_driver.py'), '--tokens', '256',
+         '--output', str(tmp_path / 'sabotaged.json')],
+        env=dict(os.environ, FGA_STAGE_SABOTAGE='shared-output', FGA_STAGE_THREADS='2'), cwd=ROOT,
+        capture_output=True, text=True, timeout=900)
+    assert result.returncode != 0
+    assert 'untyped_storage().data_ptr() != buffer.untyped_storage().data_ptr()' in result.stderr + result.stdout
