@@ -18,6 +18,27 @@ for path in (ROOT, PACKAGE):
         sys.path.insert(0, path)
 
 
+def pytest_collection_finish(session):
+    session.config._fga_staged = any(
+        item.fspath.basename == 'test_reference_programs_staged.py' and 'passes_on_the_cpu_stage' in item.name
+        for item in session.items)
+
+
+def pytest_runtest_setup(item):
+    # The staged reference programs (minutes of CPU work in processes of their own) start when the long
+    # simulated-rank tests begin and run beside them; their own test file then only collects results.
+    if getattr(item.config, '_fga_staged', False) and item.fspath.basename == 'test_host_simulated_ranks.py':
+        item.config._fga_staged = False
+        import importlib
+        importlib.import_module('tests.test_reference_programs_staged').start_all()   # the name pytest imports it by
+
+
+def pytest_sessionfinish(session, exitstatus):
+    staged = sys.modules.get('tests.test_reference_programs_staged')
+    if staged is not None:
+        staged.stop_all()
+
+
 def pytest_configure(config):
     config.addinivalue_line('markers', 'gpu: needs a B200 (sm_100a) GPU')
 

@@ -12,8 +12,9 @@ pipeline-parallel set-up order, and correct values after graph replays with chan
 by the reference's own independent FP32 computations. It says nothing about the CUDA kernels;
 tests/test_zu_reference_drivers.py runs the same programs on GPUs.
 
-All programs are started together when the first test asks for one (they are independent processes
-with two threads each), so the file costs about as long as its slowest program. FGA_STAGED=all adds the
+All programs are started together (they are independent processes with two threads each) - by
+tests/conftest.py when the long simulated-rank tests of the suite begin, else when the first test here
+asks for one - so the file costs about as long as its slowest program, or nothing. FGA_STAGED=all adds the
 long ones (minutes each on eight cores).
 """
 import os
@@ -76,30 +77,23 @@ NEEDS_OUTPUT = {'benchmark/run.py', 'tests/attention_training_driver.py', 'tests
                 'tests/mxfp8_driver.py', 'tests/mxfp8_local_driver.py', 'tests/variable_length_driver.py'}
 
 
-class Finished:
-    """A program that has already ended, with the interface of the process objects the tests wait on."""
-
-    def __init__(self, returncode, output):
-        self.returncode, self.output = returncode, output
-
-    def communicate(self, timeout=None):
-        return self.output, None
-
-    def poll(self):
-        return self.returncode
-
-
 def selected():
     everything = os.environ.get('FGA_STAGED', '') == 'all'
     return [name for name, spec in PROGRAMS.items() if spec[-1] or everything]
 
 
-@pytest.fixture(scope='module')
-def running(tmp_path_factory):
-    """Every selected program as a process tree of its own, all started now."""
-    scratch = tmp_path_factory.mktemp('staged')
+STARTED = {}      # name -> (process, path of its output file); filled once per session
+
+
+def start_all():
+    """Every selected program as a process tree of its own, all started now (output to files, so that
+    nobody has to read a pipe while they run). tests/conftest.py calls this early, when the long
+    simulated-rank tests begin, so that the programs run beside those instead of after them."""
+    import tempfile
+    if STARTED or not os.path.exists(os.path.join(STAGED, 'benchmark', 'run.py')):
+        return STARTED
+    scratch = tempfile.mkdtemp(prefix='fga-staged-')
     env = dict(os.environ, FGA_STAGE_THREADS='2')
-    started = {}
     # The pipeline driver gives its process group 75 s per collective: it runs first, alone (seconds), so
     # that a loaded machine cannot push it over that limit; everything else then starts together.
     order = sorted(selected(), key=lambda name: name != 'pipeline_setup')
@@ -109,28 +103,40 @@ def running(tmp_path_factory):
                    program if program == '-m' else os.path.join(ROOT if program == 'bench.py' else STAGED, program),
                    *arguments]
         if program in NEEDS_OUTPUT:
-            command += ['--output', str(scratch / f'{name}.json')]
-        started[name] = subprocess.Popen(command, env=env, cwd=ROOT, stdout=subprocess.PIPE,
-                                         stderr=subprocess.STDOUT, text=True)
+            command += ['--output', os.path.join(scratch, f'{name}.json')]
+        log = os.path.join(scratch, f'{name}.log')
+        with open(log, 'w') as sink:
+            STARTED[name] = (subprocess.Popen(command, env=env, cwd=ROOT, stdout=sink, stderr=subprocess.STDOUT), log)
         if name == 'pipeline_setup':
-            output, _ = started[name].communicate(timeout=600)
-            started[name] = Finished(started[name].returncode, output)
-    yield started
-    for process in started.values():
+            STARTED[name][0].wait(timeout=600)
+    return STARTED
+
+
+def stop_all():
+    for process, _ in STARTED.values():
         if process.poll() is None:
             process.kill()
-            process.communicate()
+            process.wait()
+
+
+@pytest.fixture(scope='module')
+def running():
+    yield start_all()
+    stop_all()
 
 
 @pytest.mark.parametrize('name', selected())
 def test_reference_program_passes_on_the_cpu_stage(running, name):
-    process = running[name]
+    process, log = running[name]
     try:
-        output, _ = process.communicate(timeout=3000)
+        process.wait(timeout=3000)
     except subprocess.TimeoutExpired:
         process.kill()
-        output, _ = process.communicate()
-        pytest.fail(f'{name}: no end after 3000 s\n{output[-3000:]}')
+        process.wait()
+        with open(log) as text:
+            pytest.fail(f'{name}: no end after 3000 s\n{text.read()[-3000:]}')
+    with open(log) as text:
+        output = text.read()
     assert process.returncode == 0, f'{name} exited {process.returncode}\n{output[-4000:]}'
     assert PROGRAMS[name][4] in output, output[-2000:]
     assert ' failed' not in output.splitlines()[-1], output[-2000:]
