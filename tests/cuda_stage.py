@@ -59,7 +59,7 @@ def _not_while_capturing(what):
     """A real capture fails on anything that waits for the device or reads device memory from the
     host; the emulation refuses the same, outside the simulated launches (which are host code here)."""
     recording = STATE.recording
-    if recording is not None and not recording.inside_launch and not recording.replaying:
+    if recording is not None and not recording.inside_launch:
         raise RuntimeError(f'{what}: operation not permitted while a stream is capturing (emulated capture)')
 
 
@@ -110,7 +110,6 @@ class Recording(TorchDispatchMode):
         super().__init__()
         self.nodes = []
         self.inside_launch = False
-        self.replaying = False
 
     def __torch_dispatch__(self, func, types_, args=(), kwargs=None):
         kwargs = kwargs or {}
