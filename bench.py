@@ -988,7 +988,10 @@ def run_gpu_arm(args):
         if e2e is not None:
             line['e2e'] = e2e
         if world == 1 and args.impl == 'fused' and not args.no_cpu_baseline:
-            line['cpu_baseline'], _ = cpu_unfused_sample(hidden, heads, segments, args.cpu_sample_tokens, 2, 1)
+            try:
+                line['cpu_baseline'], _ = cpu_unfused_sample(hidden, heads, segments, args.cpu_sample_tokens, 2, 1)
+            except Exception as error:     # the device measurements above must not be lost to the host-side leg
+                line['cpu_baseline'] = dict(value=None, unit=UNIT, unavailable=f'{type(error).__name__}: {str(error)[:300]}')
         print(json.dumps(line), flush=True)
     # ---- leave together: every rank drains its device and gives its symmetric buffers back
     fence()
@@ -1101,10 +1104,6 @@ def end_to_end(torch, api, args, inputs, state, step, fence, max_over_ranks, wor
     step k+1's copy overlaps step k's compute) and every step's results - y and every gradient the
     caller receives (dx, dW_qkv, dO, dW_o) - travel back to pinned host memory (second copy stream,
     double-buffered device staging). The first copy is issued after the start event."""
-    host_in = [api.pin(t.detach().to('cpu')) for t in inputs]
-    h2d_bytes = sum(t.numel() * t.element_size() for t in host_in)
-    staged_in = [[torch.empty_like(t.detach()) for t in inputs] for _ in range(2)]
-
     def step_results():
         return [state['y'], state['dq'][0], *_tensors(state['dq'][1]), state['do'][0], *_tensors(state['do'][1])]
 
@@ -1114,9 +1113,24 @@ def end_to_end(torch, api, args, inputs, state, step, fence, max_over_ranks, wor
     step()                                   # results of the final launch mode exist: size the buffers
     api.synchronize()
     shapes = [t.detach() for t in step_results()]
-    staged_out = [[torch.empty_like(t) for t in shapes] for _ in range(2)]
-    host_out = [[api.pin(torch.empty(t.shape, dtype=t.dtype)) for t in shapes] for _ in range(2)]
+    h2d_bytes = sum(t.numel() * t.element_size() for t in inputs)
     d2h_bytes = sum(t.numel() * t.element_size() for t in shapes)
+    # Pinned host buffers (inputs once, results twice) and device staging (both twice). A host that cannot
+    # pin that much must not cost the run its line: every rank reports, and if any could not, all skip the leg.
+    problem = ''
+    try:
+        host_in = [api.pin(t.detach().to('cpu')) for t in inputs]
+        staged_in = [[torch.empty_like(t.detach()) for t in inputs] for _ in range(2)]
+        staged_out = [[torch.empty_like(t) for t in shapes] for _ in range(2)]
+        host_out = [[api.pin(torch.empty(t.shape, dtype=t.dtype)) for t in shapes] for _ in range(2)]
+    except (RuntimeError, MemoryError) as error:
+        problem = f'{type(error).__name__}: {str(error)[:200]}'
+        host_in = staged_in = staged_out = host_out = None
+    failed, = max_over_ranks([1.0 if problem else 0.0])
+    if failed:
+        return dict(value=None, unit=UNIT, h2d_bytes_per_step=h2d_bytes, d2h_bytes_per_step=d2h_bytes,
+                    unavailable='the staging buffers of the end-to-end leg could not be allocated on every rank'
+                                + (f' ({problem})' if problem else ''))
     h2d_stream, d2h_stream = api.Stream(), api.Stream()
     ready = [api.Event() for _ in range(2)]          # inputs of the slot are on the device
     consumed = [api.Event() for _ in range(2)]       # the step has taken them over

@@ -142,6 +142,27 @@ def test_harness_control_flow_on_two_cpu_ranks(extra):
     assert 'samples' in line['clocks'] and 'roofline' not in line    # the kernel roofline belongs to the fused arm
 
 
+@pytest.mark.timeout(300)
+def test_end_to_end_leg_is_skipped_not_fatal_when_its_buffers_cannot_be_pinned():
+    """A host that cannot pin the staging buffers of the end-to-end leg still gets its line: the leg
+    reports why it is missing, everything else is measured."""
+    script = (
+        'import sys, bench\n'
+        'def refuse(tensor):\n'
+        '    raise RuntimeError("CUDA error: out of memory (pinning refused by the test)")\n'
+        'bench.HostApi.pin = staticmethod(refuse)\n'
+        'sys.argv = ["bench.py", "--impl", "nccl", "--device", "cpu", "--tokens", "512", "--hidden", "512", "--heads", "4",\n'
+        '            "--steps", "2", "--warmup", "1", "--min-seconds", "0.1", "--no-cpu-baseline"]\n'
+        'bench.guarded_main()\n')
+    run = subprocess.run([sys.executable, '-c', script], capture_output=True, text=True, timeout=280, cwd=ROOT,
+                         env=dict(os.environ, MASTER_ADDR='127.0.0.1', MASTER_PORT='29796'))
+    assert run.returncode == 0, run.stderr[-3000:]
+    line = json.loads([text for text in run.stdout.splitlines() if text.startswith('{')][-1])
+    assert line['value'] > 0 and line['parity_check']['passed']
+    assert line['e2e']['value'] is None and 'pinning refused' in line['e2e']['unavailable']
+    assert line['e2e']['h2d_bytes_per_step'] > 0 and line['e2e']['d2h_bytes_per_step'] > 0
+
+
 def test_kernel_roofline_from_instrumented_steps():
     """The per-launch bookkeeping of the fused arm with stand-ins for the host layer: ten eager steps
     are instrumented, the first two are dropped, GEMM launches carry algorithmic FLOPs (pad rows not
